@@ -1,0 +1,365 @@
+"""DCI / MDCI: the reference's Python operator surface on the B200-native engine.
+
+Mirrors dciknn_cuda/core.py of the reference (DCI: lines 25-107, MDCI: lines
+110-169): same constructor arguments, same methods (add, query, clear, reset,
+free), same argument checks and exception types, same return convention (a
+pair of [num_queries, k] float32 CUDA tensors: neighbour ids, then Euclidean
+distances, rows ascending by distance).  Everything below this file is the C
+ABI of include/dci_b200.h; torch only supplies device memory and streams.
+
+Extras, all keyword-only and defaulting to the reference's behaviour:
+  seed / proj           choose or inject the projection directions (the reference
+                        draws them from the process-global rand(), util_kernel.cu:124-127)
+  max_num_candidates    the reference hard-codes 10 * num_neighbours (core.py:87, :141)
+  MDCI(process_group=)  one process per GPU over torch.distributed instead of one
+                        process driving every device
+"""
+import ctypes as C
+import itertools
+import os
+
+import torch
+
+from . import _capi
+
+_seed_counter = itertools.count(1)
+
+
+def _default_seed():
+    # a fresh stream of directions per instance, like the reference, where every
+    # _dci_new advances rand(); deterministic per process unless DCI_B200_SEED moves it
+    base = int(os.environ.get("DCI_B200_SEED", "0"))
+    return (base * 0x9E3779B97F4A7C15 + next(_seed_counter)) & 0xFFFFFFFFFFFFFFFF
+
+
+def _device_index(device):
+    if isinstance(device, torch.device):
+        if device.type != "cuda":
+            raise TypeError("device must be a cuda device")
+        return torch.cuda.current_device() if device.index is None else device.index
+    if isinstance(device, str):
+        return _device_index(torch.device(device))
+    return int(device)
+
+
+def _stream_ptr(dev):
+    return C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+class DCI(object):
+    """Prioritized DCI on one GPU (reference: dciknn_cuda/core.py:25-107)."""
+
+    def __init__(self, dim, num_comp_indices=2, num_simp_indices=7, bs=100, ts=10, device=0, *,
+                 seed=None, proj=None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("DCI CUDA version requires GPU access, please check CUDA driver.")
+        self._dim = dim
+        self._num_comp_indices = num_comp_indices
+        self._num_simp_indices = num_simp_indices
+        self._block_size = bs
+        self._thread_size = ts
+        self._device = _device_index(device)
+        self._array = None
+        self.num_points = 0
+        self._handle = C.c_void_p()
+        lib = _capi.lib()
+        _capi.check(lib.dci_b200_create(C.byref(self._handle), dim, num_comp_indices, num_simp_indices,
+                                        self._device, _default_seed() if seed is None else int(seed)))
+        if proj is not None:
+            self.set_proj(proj)
+
+    # -- properties of the reference class (core.py:41-51)
+    @property
+    def dim(self):
+        return self._dim
+
+    @property
+    def num_comp_indices(self):
+        return self._num_comp_indices
+
+    @property
+    def num_simp_indices(self):
+        return self._num_simp_indices
+
+    @property
+    def device(self):
+        return torch.device("cuda", self._device)
+
+    def _ensure_positive_integer(self, x):
+        if not isinstance(x, int):
+            raise TypeError("number must be an integer")
+        elif x <= 0:
+            raise ValueError("number must be positive")
+
+    def _check_data(self, arr):
+        # same checks, order and exception types as core.py:59-67
+        if arr.shape[1] != self.dim:
+            raise ValueError("mismatch between tensor dimension (%d) and the declared dimension of this DCI instance (%d)" % (arr.shape[1], self.dim))
+        if arr.dtype != torch.float:
+            raise TypeError("tensor must consist of single-precision floats")
+        if not arr.is_contiguous():
+            raise ValueError("the memory layout of tensor must be in row-major (C-order)")
+        if not arr.is_cuda:
+            raise TypeError("tensor must be a cuda tensor")
+        if arr.device.index != self._device:
+            raise ValueError("tensor lives on %s but this DCI instance was created on cuda:%d" % (arr.device, self._device))
+
+    def _live(self):
+        if not self._handle:
+            raise RuntimeError("this DCI instance has been freed")
+        return self._handle
+
+    # -- directions (no counterpart in the reference's Python API)
+    def get_proj(self):
+        """The L*S unit directions as a [L*S, dim] float32 CPU tensor (row h + m*S)."""
+        out = torch.empty(self._num_comp_indices * self._num_simp_indices, self._dim, dtype=torch.float32)
+        _capi.check(_capi.lib().dci_b200_get_proj(self._live(), C.c_void_p(out.data_ptr())))
+        return out
+
+    def set_proj(self, proj):
+        proj = torch.as_tensor(proj, dtype=torch.float32).cpu().contiguous()
+        if tuple(proj.shape) != (self._num_comp_indices * self._num_simp_indices, self._dim):
+            raise ValueError("proj must have shape [num_comp_indices * num_simp_indices, dim]")
+        rc = _capi.lib().dci_b200_set_proj(self._live(), C.c_void_p(proj.data_ptr()))
+        if rc == _capi.ERR_STATE:
+            raise RuntimeError(_capi.lib().dci_b200_last_error().decode())
+        _capi.check(rc)
+
+    # -- reference methods
+    def add(self, data):
+        if self.num_points > 0:
+            raise RuntimeError("DCI class does not support insertion of more than one tensor. Must combine all tensors into one tensor before inserting")
+        self._check_data(data)
+        if data.shape[0] == 0:
+            raise ValueError("cannot add an empty tensor")
+        with torch.cuda.device(self._device):
+            _capi.check(_capi.lib().dci_b200_add(self._live(), C.c_void_p(data.data_ptr()), data.shape[0],
+                                                self._block_size, self._thread_size, _stream_ptr(self._device)))
+        self.num_points = data.shape[0]
+        self._array = data          # the index borrows the tensor's memory
+
+    def query(self, query, num_neighbours=-1, num_outer_iterations=5000, blind=False, *,
+              max_num_candidates=None, return_int_ids=False):
+        """query is [num_queries, dim] (or [dim]); returns ([num_queries, k] ids, [num_queries, k] distances)."""
+        if len(query.shape) < 2:
+            _query = query.unsqueeze(0)
+        else:
+            _query = query
+        self._check_data(_query)
+        if num_neighbours < 0:
+            num_neighbours = self.num_points
+        self._ensure_positive_integer(num_neighbours)
+        if blind:
+            raise NotImplementedError("blind querying is not supported")
+        if max_num_candidates is None:
+            max_num_candidates = 10 * num_neighbours
+        if self.num_points == 0:
+            raise RuntimeError("the index is empty; add data first")
+        nq = _query.shape[0]
+        with torch.cuda.device(self._device):
+            ids = torch.empty((nq, num_neighbours), dtype=torch.int32, device=_query.device)
+            dists = torch.empty((nq, num_neighbours), dtype=torch.float32, device=_query.device)
+            _capi.check(_capi.lib().dci_b200_query(
+                self._live(), C.c_void_p(_query.data_ptr()), nq, num_neighbours, int(num_outer_iterations),
+                int(max_num_candidates), 0, self._block_size, self._thread_size,
+                C.c_void_p(ids.data_ptr()), C.c_void_p(dists.data_ptr()), _stream_ptr(self._device)))
+            if return_int_ids:
+                return ids, dists
+            return ids.to(torch.float32), dists     # the reference returns ids as float32 (dci_cuda.cpp:111)
+
+    def query_host(self, query, num_neighbours, num_outer_iterations=5000, *, max_num_candidates=None):
+        """Same query from and to HOST memory through dci_b200_query_host: `query`
+        is a CPU float32 tensor; returns CPU (int32 ids, float32 distances)."""
+        q = query.reshape(-1, self._dim)
+        if q.dtype != torch.float32 or q.is_cuda or not q.is_contiguous():
+            raise TypeError("query_host takes a contiguous float32 CPU tensor")
+        self._ensure_positive_integer(num_neighbours)
+        if max_num_candidates is None:
+            max_num_candidates = 10 * num_neighbours
+        ids = torch.empty((q.shape[0], num_neighbours), dtype=torch.int32)
+        dists = torch.empty((q.shape[0], num_neighbours), dtype=torch.float32)
+        _capi.check(_capi.lib().dci_b200_query_host(
+            self._live(), C.c_void_p(q.data_ptr()), q.shape[0], num_neighbours, int(num_outer_iterations),
+            int(max_num_candidates), 0, self._block_size, self._thread_size,
+            C.c_void_p(ids.data_ptr()), C.c_void_p(dists.data_ptr())))
+        return ids, dists
+
+    def clear(self):
+        _capi.check(_capi.lib().dci_b200_clear(self._live()))
+        self.num_points = 0
+        self._array = None
+
+    def reset(self, *, seed=None):
+        _capi.check(_capi.lib().dci_b200_reset(self._live(), _default_seed() if seed is None else int(seed)))
+        self.num_points = 0
+        self._array = None
+
+    def free(self):
+        if self._handle:
+            _capi.lib().dci_b200_destroy(self._handle)
+            self._handle = C.c_void_p()
+        self.num_points = 0
+        self._array = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+    # -- inspection helpers used by tests and the benchmark
+    def get_index(self):
+        """(keys, ids): [L*S, N] float32 / int32 CPU tensors, each partition's segment sorted."""
+        I = self._num_comp_indices * self._num_simp_indices
+        keys = torch.empty(I, self.num_points, dtype=torch.float32)
+        ids = torch.empty(I, self.num_points, dtype=torch.int32)
+        _capi.check(_capi.lib().dci_b200_get_index(self._live(), C.c_void_p(keys.data_ptr()), C.c_void_p(ids.data_ptr())))
+        return keys, ids
+
+    def project(self, x):
+        """[L*S, n] projected keys of the rows of x (exact fp32 path)."""
+        self._check_data(x)
+        I = self._num_comp_indices * self._num_simp_indices
+        out = torch.empty(I, x.shape[0], dtype=torch.float32, device=x.device)
+        with torch.cuda.device(self._device):
+            _capi.check(_capi.lib().dci_b200_project(self._live(), C.c_void_p(x.data_ptr()), x.shape[0],
+                                                    C.c_void_p(out.data_ptr()), _stream_ptr(self._device)))
+        return out
+
+    def enable_work_stats(self, on=True):
+        _capi.check(_capi.lib().dci_b200_enable_work_stats(self._live(), 1 if on else 0))
+
+    def get_work_stats(self, num_queries):
+        """[num_queries, P, 6] int64: stop iteration, windows, entries, promoted, lane-0 promotions, exhausted."""
+        out = torch.zeros(num_queries, self._block_size, 6, dtype=torch.int64)
+        _capi.check(_capi.lib().dci_b200_get_work_stats(self._live(), C.c_void_p(out.data_ptr()),
+                                                       num_queries * self._block_size))
+        return out
+
+    def launch_count(self):
+        return int(_capi.lib().dci_b200_launch_count(self._live()))
+
+
+def shard_bounds(num_points, num_shards):
+    """Row ranges of MDCI's shards (reference core.py:122-125): shard i holds
+    rows [i*dpd, (i+1)*dpd) clipped to num_points, dpd = num_points // D + 1."""
+    dpd = num_points // num_shards + 1
+    return dpd, [(min(i * dpd, num_points), min((i + 1) * dpd, num_points)) for i in range(num_shards)]
+
+
+def merge_shards(ids, dists, offsets, k):
+    """ids/dists: [D, nq, k] int32/float32 CUDA tensors of per-shard results;
+    returns ([nq, k] int64 global ids, [nq, k] float32) -- the k smallest per
+    query, ties to the lower global id (reference core.py:153-157)."""
+    D, nq, kk = ids.shape
+    assert kk == k and dists.shape == ids.shape and ids.is_cuda and ids.is_contiguous() and dists.is_contiguous()
+    dev = ids.device.index
+    out_ids = torch.empty((nq, k), dtype=torch.int64, device=ids.device)
+    out_dists = torch.empty((nq, k), dtype=torch.float32, device=ids.device)
+    offs = (C.c_longlong * D)(*[int(o) for o in offsets])
+    with torch.cuda.device(dev):
+        _capi.check(_capi.lib().dci_b200_merge_shards(
+            C.c_void_p(ids.data_ptr()), C.c_void_p(dists.data_ptr()), D, nq, k, offs,
+            C.c_void_p(out_ids.data_ptr()), C.c_void_p(out_dists.data_ptr()), dev, _stream_ptr(dev)))
+    return out_ids, out_dists
+
+
+class MDCI(object):
+    """Prioritized DCI sharded over several GPUs (reference: core.py:110-169).
+
+    Two ways to run it:
+      * MDCI(dim, ..., devices=[0, 1, ...]): one process drives every device, as
+        the reference does; results land on devices[0].
+      * MDCI(dim, ..., process_group=pg): one process per GPU (torch.distributed,
+        NCCL); every rank calls add/query with the same arguments, holds shard
+        `rank` on its current device and receives the merged result.
+    Every shard answers every query with its local top-k; the lists are gathered
+    and merged on the device by dci_b200_merge_shards.
+    """
+
+    def __init__(self, dim, num_comp_indices=2, num_simp_indices=7, bs=100, ts=10, devices=[0], *,
+                 process_group=None, seeds=None, projs=None, _local_engine=None, _merge=None):
+        self._dim = dim
+        self._pg = process_group
+        self._merge = merge_shards if _merge is None else _merge
+        self.data_per_device = 0
+        if process_group is None:
+            self.devices = [_device_index(d) for d in devices]
+            self.num_devices = len(self.devices)
+            self.dcis = [DCI(dim, num_comp_indices, num_simp_indices, bs, ts, dev,
+                             seed=None if seeds is None else seeds[i],
+                             proj=None if projs is None else projs[i])
+                         for i, dev in enumerate(self.devices)]
+        else:
+            import torch.distributed as dist
+            self._dist = dist
+            self.rank = dist.get_rank(process_group)
+            self.num_devices = dist.get_world_size(process_group)
+            if _local_engine is not None:
+                self.dcis = [_local_engine]
+            else:
+                dev = torch.cuda.current_device()
+                self.devices = [dev]
+                self.dcis = [DCI(dim, num_comp_indices, num_simp_indices, bs, ts, dev,
+                                 seed=None if seeds is None else seeds[self.rank],
+                                 proj=None if projs is None else projs[self.rank])]
+
+    def add(self, data):
+        dpd, bounds = shard_bounds(data.shape[0], self.num_devices)
+        self.data_per_device = dpd
+        if self._pg is None:
+            for i, dev in enumerate(self.devices):
+                lo, hi = bounds[i]
+                self.dcis[i].add(data[lo:hi].to(torch.device("cuda", dev)).contiguous())
+        else:
+            lo, hi = bounds[self.rank]
+            shard = data[lo:hi]
+            eng = self.dcis[0]
+            if isinstance(eng, DCI):
+                shard = shard.to(eng.device).contiguous()
+            eng.add(shard)
+
+    def query(self, query, num_neighbours=-1, num_outer_iterations=5000, blind=False, *,
+              max_num_candidates=None, return_int_ids=False):
+        if num_neighbours <= 0:
+            raise RuntimeError('num_neighbours must be positive')
+        if blind:
+            raise NotImplementedError("blind querying is not supported")
+        _query = query.unsqueeze(0) if len(query.shape) < 2 else query
+        k = num_neighbours
+        if self._pg is None:
+            ids, dists = [], []
+            home = torch.device("cuda", self.devices[0])
+            for i, dev in enumerate(self.devices):
+                q = _query.to(torch.device("cuda", dev)).contiguous()
+                a, d = self.dcis[i].query(q, k, num_outer_iterations, max_num_candidates=max_num_candidates,
+                                          return_int_ids=True)
+                ids.append(a)
+                dists.append(d)
+            ids = torch.stack([a.to(home) for a in ids]).contiguous()
+            dists = torch.stack([d.to(home) for d in dists]).contiguous()
+        else:
+            eng = self.dcis[0]
+            q = _query.to(eng.device).contiguous() if isinstance(eng, DCI) else _query
+            a, d = eng.query(q, k, num_outer_iterations, max_num_candidates=max_num_candidates, return_int_ids=True)
+            ids = torch.empty((self.num_devices,) + tuple(a.shape), dtype=a.dtype, device=a.device)
+            dists = torch.empty((self.num_devices,) + tuple(d.shape), dtype=d.dtype, device=d.device)
+            self._dist.all_gather_into_tensor(ids, a.contiguous(), group=self._pg)
+            self._dist.all_gather_into_tensor(dists, d.contiguous(), group=self._pg)
+        offsets = [self.data_per_device * i for i in range(self.num_devices)]
+        out_ids, out_dists = self._merge(ids, dists, offsets, k)
+        if return_int_ids:
+            return out_ids, out_dists
+        return out_ids.to(torch.float32), out_dists
+
+    def clear(self):
+        for dci in self.dcis:
+            dci.clear()
+
+    def reset(self):
+        for dci in self.dcis:
+            dci.reset()
+
+    def free(self):
+        for dci in self.dcis:
+            dci.free()

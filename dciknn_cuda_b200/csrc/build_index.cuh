@@ -1,0 +1,64 @@
+// Index build: one stable radix sort per (simple index, partition) segment.
+// Replaces copy_to_indices + sort_indices (+ the recursive device quicksort)
+// of the reference (src/dci_cuda_kernel.cu:113-146, 190-247).  The result is
+// kept as two flat arrays keys[L*S][N] / ids[L*S][N] (SoA) instead of the
+// reference's array of {key, id} structs (include/dci.h:27-30).
+// Equal keys are ordered by id (the input order), which the reference leaves
+// unspecified.
+#pragma once
+#include "common.cuh"
+
+namespace dci {
+
+template <typename ValT>
+struct BuildLayout {
+    size_t hist_bytes, buf_bytes;
+    __host__ __device__ static size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
+    __host__ __device__ static BuildLayout make(int nthreads, int cap) {
+        BuildLayout l;
+        l.hist_bytes = align16((size_t)256 * (nthreads / 32) * sizeof(ValT));
+        l.buf_bytes = align16((size_t)cap * 4) * 2 + align16((size_t)cap * sizeof(ValT)) * 2;
+        return l;
+    }
+};
+
+// Persistent CTAs; CTA c sorts segments c, c + gridDim.x, ...
+// SMEM: the ping-pong buffers live in dynamic shared memory; otherwise in the
+// CTA's slab of `gscratch`.
+template <typename ValT, bool SMEM>
+__global__ void __launch_bounds__(1024)
+build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_indices, int ppb,
+                      int num_parts, float *__restrict__ skeys, int *__restrict__ sids,
+                      unsigned char *gscratch, size_t gscratch_per_cta) {
+    extern __shared__ __align__(16) unsigned char dyn_smem[];
+    __shared__ uint32_t warp_tot[32];
+    const BuildLayout<ValT> lay = BuildLayout<ValT>::make(blockDim.x, ppb);
+    ValT *hist = reinterpret_cast<ValT *>(dyn_smem);
+    unsigned char *big = SMEM ? dyn_smem + lay.hist_bytes : gscratch + (size_t)blockIdx.x * gscratch_per_cta;
+    const size_t kbytes = BuildLayout<ValT>::align16((size_t)ppb * 4);
+    const size_t vbytes = BuildLayout<ValT>::align16((size_t)ppb * sizeof(ValT));
+    uint32_t *kA = reinterpret_cast<uint32_t *>(big);
+    uint32_t *kB = reinterpret_cast<uint32_t *>(big + kbytes);
+    ValT *vA = reinterpret_cast<ValT *>(big + 2 * kbytes);
+    ValT *vB = reinterpret_cast<ValT *>(big + 2 * kbytes + vbytes);
+    const long long nseg = (long long)num_indices * num_parts;
+    for (long long seg = blockIdx.x; seg < nseg; seg += gridDim.x) {
+        const int i = (int)(seg / num_parts), b = (int)(seg % num_parts);
+        const long long lo = (long long)b * ppb;
+        const int n = (int)min((long long)ppb, (long long)N - lo);
+        const size_t row = (size_t)i * N + lo;
+        for (int x = threadIdx.x; x < n; x += blockDim.x) {
+            kA[x] = float_to_ordered(keys_unsorted[row + x]);
+            vA[x] = (ValT)x;
+        }
+        __syncthreads();
+        cta_radix_sort<ValT, ValT, false>(kA, vA, kB, vB, n, hist, warp_tot, (ValT *)nullptr);
+        for (int x = threadIdx.x; x < n; x += blockDim.x) {
+            skeys[row + x] = ordered_to_float(kA[x]);
+            sids[row + x] = (int)(lo + vA[x]);
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace dci

@@ -1,0 +1,459 @@
+// C ABI and host orchestration of the B200-native Prioritized DCI engine.
+// The declarations and their relation to the reference's API are in
+// include/dci_b200.h.  Replaces the host side of the reference:
+// dci_init/dci_add/dci_query/dci_clear/dci_reset/dci_free
+// (src/dci_cuda_kernel.cu:93-110, 149-187, 777-899) and the Torch shim
+// (src/dci_cuda.cpp:54-173).
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <new>
+
+#include "../../include/dci_b200.h"
+#include "build_index.cuh"
+#include "common.cuh"
+#include "directions.cuh"
+#include "project.cuh"
+#include "traverse.cuh"
+
+namespace {
+
+thread_local char g_err[1024] = "";
+
+int fail(int code, const char *fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define DCI_CUDA(call)                                                                     \
+    do {                                                                                   \
+        cudaError_t e_ = (call);                                                           \
+        if (e_ != cudaSuccess)                                                             \
+            return fail(DCI_B200_ERR_CUDA, "%s failed at %s:%d: %s", #call, __FILE__,      \
+                        __LINE__, cudaGetErrorString(e_));                                 \
+    } while (0)
+
+struct Buf {
+    void *p = nullptr;
+    size_t cap = 0;
+    cudaError_t ensure(size_t bytes) {
+        if (bytes <= cap) return cudaSuccess;
+        if (p) { cudaFree(p); p = nullptr; cap = 0; }
+        cudaError_t e = cudaMalloc(&p, bytes);
+        if (e == cudaSuccess) cap = bytes;
+        return e;
+    }
+    void release() { if (p) cudaFree(p); p = nullptr; cap = 0; }
+};
+
+struct DeviceGuard {
+    int prev = -1;
+    bool ok = false;
+    explicit DeviceGuard(int dev) {
+        if (cudaGetDevice(&prev) != cudaSuccess) return;
+        ok = (prev == dev) || cudaSetDevice(dev) == cudaSuccess;
+    }
+    ~DeviceGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+
+int next_pow2(int x) { int p = 1; while (p < x) p <<= 1; return p; }
+
+}  // namespace
+
+struct dci_b200 {
+    int dim = 0, L = 0, S = 0, device = 0;
+    int num_points = 0, P = 0, T = 0, ppb = 0, num_parts = 0;
+    const float *d_data = nullptr;       // borrowed
+    float *d_proj = nullptr;             // [L*S][dim]
+    Buf keys, ids;                       // [L*S][N] sorted index
+    Buf tmp_keys, qproj, part_topk, scratch, stats, hq, hids, hdists;
+    int stats_on = 0, stats_nq = 0;
+    long long launches = 0;
+    int sm_count = 0;
+    size_t smem_optin = 0, smem_per_sm = 0;
+};
+
+namespace {
+
+int launch_directions(dci_b200 *h, unsigned long long seed, cudaStream_t st) {
+    dci::gen_directions_kernel<<<h->L * h->S, 128, 0, st>>>(h->d_proj, h->dim, seed);
+    h->launches++;
+    DCI_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cudaStream_t st) {
+    if (n <= 0) return 0;
+    const int I = h->L * h->S;
+    const unsigned grid = (unsigned)((n + dci::kProjPoints - 1) / dci::kProjPoints);
+    if (I <= 8)
+        dci::project_exact_kernel<8><<<grid, dci::kProjPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
+    else if (I <= 16 || (I > 24 && I <= 32))
+        dci::project_exact_kernel<16><<<grid, dci::kProjPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
+    else
+        dci::project_exact_kernel<12><<<grid, dci::kProjPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
+    h->launches++;
+    DCI_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <typename ValT>
+int launch_build(dci_b200 *h, const float *d_unsorted, cudaStream_t st) {
+    const int I = h->L * h->S;
+    const int nthreads = h->ppb >= 4096 ? 1024 : (h->ppb >= 1024 ? 512 : 256);
+    const auto lay = dci::BuildLayout<ValT>::make(nthreads, h->ppb);
+    const long long nseg = (long long)I * h->num_parts;
+    const size_t static_smem = 256;
+    const bool smem = lay.hist_bytes + lay.buf_bytes + static_smem <= h->smem_optin;
+    if (smem) {
+        auto kern = dci::build_segments_kernel<ValT, true>;
+        const size_t dyn = lay.hist_bytes + lay.buf_bytes;
+        DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+        int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + 1024), 2048 / nthreads));
+        const unsigned grid = (unsigned)std::min<long long>(nseg, (long long)h->sm_count * per_sm);
+        kern<<<grid, nthreads, dyn, st>>>(d_unsorted, h->num_points, I, h->ppb, h->num_parts,
+                                          (float *)h->keys.p, (int *)h->ids.p, nullptr, 0);
+    } else {
+        auto kern = dci::build_segments_kernel<ValT, false>;
+        const unsigned grid = (unsigned)std::min<long long>(nseg, (long long)h->sm_count * (2048 / nthreads));
+        DCI_CUDA(h->scratch.ensure(lay.buf_bytes * grid));
+        kern<<<grid, nthreads, lay.hist_bytes, st>>>(d_unsorted, h->num_points, I, h->ppb, h->num_parts,
+                                                     (float *)h->keys.p, (int *)h->ids.p,
+                                                     (unsigned char *)h->scratch.p, lay.buf_bytes);
+    }
+    h->launches++;
+    DCI_CUDA(cudaGetLastError());
+    return 0;
+}
+
+template <typename ValT>
+int launch_traverse(dci_b200 *h, dci::TraverseParams prm, int nthreads, cudaStream_t st) {
+    const auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb);
+    const long long nwork = (long long)prm.nq * prm.num_parts;
+    cudaFuncAttributes fa;
+    DCI_CUDA(cudaFuncGetAttributes(&fa, dci::traverse_kernel<ValT, true>));
+    const size_t static_smem = fa.sharedSizeBytes;
+    if (lay.fixed_bytes + static_smem > h->smem_optin)
+        return fail(DCI_B200_ERR_UNSUPPORTED, "dim=%d with k=%d needs %zu bytes of shared memory per CTA, more than the device offers",
+                    prm.dim, prm.knn, lay.fixed_bytes + static_smem);
+    const bool smem = lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin;
+    if (smem) {
+        auto kern = dci::traverse_kernel<ValT, true>;
+        const size_t dyn = lay.fixed_bytes + lay.big_bytes;
+        DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+        const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));
+        const unsigned grid = (unsigned)std::min<long long>(nwork, (long long)h->sm_count * per_sm);
+        kern<<<grid, nthreads, dyn, st>>>(prm);
+    } else {
+        auto kern = dci::traverse_kernel<ValT, false>;
+        const size_t dyn = lay.fixed_bytes;
+        DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+        const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));
+        const unsigned grid = (unsigned)std::min<long long>(nwork, (long long)h->sm_count * per_sm);
+        DCI_CUDA(h->scratch.ensure(lay.big_bytes * grid));
+        prm.gscratch = (unsigned char *)h->scratch.p;
+        prm.gscratch_per_cta = lay.big_bytes;
+        kern<<<grid, nthreads, dyn, st>>>(prm);
+    }
+    h->launches++;
+    DCI_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int check_handle(dci_b200 *h) {
+    if (!h) return fail(DCI_B200_ERR_ARG, "null handle");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *dci_b200_last_error(void) { return g_err; }
+
+int dci_b200_abi_version(void) { return 1; }
+
+int dci_b200_create(dci_b200_t **out, int dim, int num_comp_indices, int num_simp_indices,
+                    int device, unsigned long long seed) {
+    if (!out) return fail(DCI_B200_ERR_ARG, "out is null");
+    *out = nullptr;
+    if (dim <= 0) return fail(DCI_B200_ERR_ARG, "dim must be positive, got %d", dim);
+    if (num_comp_indices <= 0 || num_simp_indices <= 0)
+        return fail(DCI_B200_ERR_ARG, "num_comp_indices and num_simp_indices must be positive, got %d and %d",
+                    num_comp_indices, num_simp_indices);
+    if ((long long)num_comp_indices * num_simp_indices > dci::kMaxIndices || num_comp_indices > 64)
+        return fail(DCI_B200_ERR_UNSUPPORTED, "at most %d simple indices in total and 64 composite indices are supported",
+                    dci::kMaxIndices);
+    int ndev = 0;
+    DCI_CUDA(cudaGetDeviceCount(&ndev));
+    if (device < 0 || device >= ndev) return fail(DCI_B200_ERR_ARG, "device %d out of range (%d devices)", device, ndev);
+    DeviceGuard g(device);
+    if (!g.ok) return fail(DCI_B200_ERR_CUDA, "cannot select device %d", device);
+    dci_b200 *h = new (std::nothrow) dci_b200();
+    if (!h) return fail(DCI_B200_ERR_CUDA, "host allocation failed");
+    h->dim = dim; h->L = num_comp_indices; h->S = num_simp_indices; h->device = device;
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) { delete h; return fail(DCI_B200_ERR_CUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e)); }
+    h->sm_count = prop.multiProcessorCount;
+    h->smem_optin = prop.sharedMemPerBlockOptin;
+    h->smem_per_sm = prop.sharedMemPerMultiprocessor;
+    e = cudaMalloc((void **)&h->d_proj, sizeof(float) * (size_t)dim * h->L * h->S);
+    if (e != cudaSuccess) { delete h; return fail(DCI_B200_ERR_CUDA, "cudaMalloc(directions): %s", cudaGetErrorString(e)); }
+    int rc = launch_directions(h, seed, 0);
+    if (rc == 0 && (e = cudaDeviceSynchronize()) != cudaSuccess)
+        rc = fail(DCI_B200_ERR_CUDA, "direction generation: %s", cudaGetErrorString(e));
+    if (rc) { cudaFree(h->d_proj); delete h; return rc; }
+    *out = h;
+    return 0;
+}
+
+int dci_b200_destroy(dci_b200_t *h) {
+    if (!h) return 0;
+    DeviceGuard g(h->device);
+    cudaDeviceSynchronize();
+    Buf *bufs[] = {&h->keys, &h->ids, &h->tmp_keys, &h->qproj, &h->part_topk, &h->scratch, &h->stats,
+                   &h->hq, &h->hids, &h->hdists};
+    for (Buf *b : bufs) b->release();
+    if (h->d_proj) cudaFree(h->d_proj);
+    delete h;
+    return 0;
+}
+
+int dci_b200_get_proj(dci_b200_t *h, float *h_out) {
+    if (int rc = check_handle(h)) return rc;
+    if (!h_out) return fail(DCI_B200_ERR_ARG, "h_out is null");
+    DeviceGuard g(h->device);
+    DCI_CUDA(cudaDeviceSynchronize());
+    DCI_CUDA(cudaMemcpy(h_out, h->d_proj, sizeof(float) * (size_t)h->dim * h->L * h->S, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int dci_b200_set_proj(dci_b200_t *h, const float *h_in) {
+    if (int rc = check_handle(h)) return rc;
+    if (!h_in) return fail(DCI_B200_ERR_ARG, "h_in is null");
+    if (h->num_points > 0) return fail(DCI_B200_ERR_STATE, "directions cannot change while the index holds points; clear first");
+    DeviceGuard g(h->device);
+    DCI_CUDA(cudaDeviceSynchronize());
+    DCI_CUDA(cudaMemcpy(h->d_proj, h_in, sizeof(float) * (size_t)h->dim * h->L * h->S, cudaMemcpyHostToDevice));
+    return 0;
+}
+
+int dci_b200_add(dci_b200_t *h, const float *d_data, int num_points, int block_size, int thread_size, void *stream) {
+    if (int rc = check_handle(h)) return rc;
+    if (h->num_points > 0)
+        return fail(DCI_B200_ERR_STATE, "the index already holds %d points; it does not support insertion of more than one array (clear first)", h->num_points);
+    if (!d_data) return fail(DCI_B200_ERR_ARG, "d_data is null");
+    if (num_points <= 0) return fail(DCI_B200_ERR_ARG, "num_points must be positive, got %d", num_points);
+    if (block_size <= 0 || thread_size <= 0)
+        return fail(DCI_B200_ERR_ARG, "block_size and thread_size must be positive, got %d and %d", block_size, thread_size);
+    if (thread_size > 65536) return fail(DCI_B200_ERR_UNSUPPORTED, "thread_size above 65536 is not supported");
+    DeviceGuard g(h->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int I = h->L * h->S;
+    const int ppb = (num_points + block_size - 1) / block_size;
+    const int num_parts = (num_points + ppb - 1) / ppb;
+    {   // encoded promotion (rank << tshift | lane) must fit 32 bits
+        int tshift = 0;
+        while ((1 << tshift) < thread_size) ++tshift;
+        const unsigned long long wcap = (unsigned long long)h->S * ((ppb + thread_size - 1) / thread_size + 2);
+        if ((wcap << tshift) >= 0xFFFFFFFFull)
+            return fail(DCI_B200_ERR_UNSUPPORTED, "partition of %d points with %d simple indices is too large", ppb, h->S);
+    }
+    const size_t n_entries = (size_t)I * num_points;
+    DCI_CUDA(h->keys.ensure(n_entries * sizeof(float)));
+    DCI_CUDA(h->ids.ensure(n_entries * sizeof(int)));
+    DCI_CUDA(h->tmp_keys.ensure(n_entries * sizeof(float)));
+    h->num_points = num_points; h->P = block_size; h->T = thread_size; h->ppb = ppb; h->num_parts = num_parts;
+    h->d_data = d_data;
+    int rc = launch_project(h, d_data, num_points, (float *)h->tmp_keys.p, st);
+    if (!rc) rc = (ppb <= 65535) ? launch_build<uint16_t>(h, (const float *)h->tmp_keys.p, st)
+                                 : launch_build<uint32_t>(h, (const float *)h->tmp_keys.p, st);
+    if (rc) { h->num_points = 0; h->d_data = nullptr; }
+    return rc;
+}
+
+int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
+                   int num_outer_iterations, int max_num_candidates, int blind, int block_size,
+                   int thread_size, int *d_ids, float *d_dists, void *stream) {
+    if (int rc = check_handle(h)) return rc;
+    if (blind) return fail(DCI_B200_ERR_UNSUPPORTED, "blind querying is not supported");
+    if (h->num_points <= 0) return fail(DCI_B200_ERR_STATE, "the index is empty; add data first");
+    if (num_queries < 0) return fail(DCI_B200_ERR_ARG, "num_queries must not be negative");
+    if (num_queries == 0) return 0;
+    if (!d_query || !d_ids || !d_dists) return fail(DCI_B200_ERR_ARG, "null query or output pointer");
+    if (num_neighbours <= 0) return fail(DCI_B200_ERR_ARG, "num_neighbours must be positive, got %d", num_neighbours);
+    if (num_neighbours > h->num_points)
+        return fail(DCI_B200_ERR_ARG, "num_neighbours (%d) exceeds the number of indexed points (%d)", num_neighbours, h->num_points);
+    if (num_neighbours > dci::kMaxTopK)
+        return fail(DCI_B200_ERR_UNSUPPORTED, "num_neighbours above %d is not supported yet", dci::kMaxTopK);
+    if (block_size != h->P || thread_size != h->T)
+        return fail(DCI_B200_ERR_ARG, "block_size/thread_size (%d, %d) differ from the values the index was built with (%d, %d)",
+                    block_size, thread_size, h->P, h->T);
+    DeviceGuard g(h->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int I = h->L * h->S;
+    DCI_CUDA(h->qproj.ensure(sizeof(float) * (size_t)I * num_queries));
+    if (int rc = launch_project(h, d_query, num_queries, (float *)h->qproj.p, st)) return rc;
+
+    dci::TraverseParams prm;
+    memset(&prm, 0, sizeof(prm));
+    prm.skeys = (const float *)h->keys.p; prm.sids = (const int *)h->ids.p; prm.data = h->d_data;
+    prm.qproj = (const float *)h->qproj.p; prm.query = d_query;
+    prm.N = h->num_points; prm.dim = h->dim; prm.L = h->L; prm.S = h->S; prm.P = h->P; prm.T = h->T;
+    prm.ppb = h->ppb; prm.num_parts = h->num_parts; prm.nq_total = num_queries;
+    prm.knn = num_neighbours; prm.max_cand = max_num_candidates;
+    prm.outer_s = (long long)num_outer_iterations * h->S;
+    prm.wcap = h->S * ((h->ppb + h->T - 1) / h->T + 2);
+    prm.tshift = 0;
+    while ((1 << prm.tshift) < h->T) ++prm.tshift;
+    prm.divT = dci::FastDiv::make((uint32_t)h->T, (uint64_t)h->ppb + 1);
+    prm.vec4 = (h->dim % 4 == 0) && (((uintptr_t)h->d_data & 15) == 0) && (((uintptr_t)d_query & 15) == 0);
+    const int nthreads = prm.wcap >= 4096 ? 1024 : (prm.wcap >= 1024 ? 512 : 256);
+    prm.topk_cap = next_pow2(num_neighbours + nthreads);
+    const int merge_threads = 256;
+    const int merge_cap = next_pow2(num_neighbours + merge_threads);
+
+    if (h->stats_on) {
+        const size_t bytes = sizeof(long long) * 6 * (size_t)num_queries * h->P;
+        DCI_CUDA(h->stats.ensure(bytes));
+        DCI_CUDA(cudaMemsetAsync(h->stats.p, 0, bytes, st));
+        prm.work_stats = (long long *)h->stats.p;
+        h->stats_nq = num_queries;
+    }
+    const size_t per_query = sizeof(uint64_t) * (size_t)h->num_parts * num_neighbours;
+    const int batch = (int)std::max<size_t>(1, std::min<size_t>((size_t)num_queries, ((size_t)1 << 30) / per_query));
+    DCI_CUDA(h->part_topk.ensure(per_query * batch));
+    prm.part_topk = (uint64_t *)h->part_topk.p;
+    for (int q0 = 0; q0 < num_queries; q0 += batch) {
+        prm.q0 = q0;
+        prm.nq = std::min(batch, num_queries - q0);
+        int rc = (prm.wcap <= 65535) ? launch_traverse<uint16_t>(h, prm, nthreads, st)
+                                     : launch_traverse<uint32_t>(h, prm, nthreads, st);
+        if (rc) return rc;
+        dci::merge_partitions_kernel<<<prm.nq, merge_threads, (size_t)merge_cap * 8, st>>>(
+            prm.part_topk, h->num_parts, num_neighbours, merge_cap, q0, d_ids, d_dists);
+        h->launches++;
+        DCI_CUDA(cudaGetLastError());
+    }
+    return 0;
+}
+
+int dci_b200_query_host(dci_b200_t *h, const float *h_query, int num_queries, int num_neighbours,
+                        int num_outer_iterations, int max_num_candidates, int blind, int block_size,
+                        int thread_size, int *h_ids, float *h_dists) {
+    if (int rc = check_handle(h)) return rc;
+    if (num_queries < 0) return fail(DCI_B200_ERR_ARG, "num_queries must not be negative");
+    if (num_queries == 0) return 0;
+    if (!h_query || !h_ids || !h_dists) return fail(DCI_B200_ERR_ARG, "null query or output pointer");
+    if (num_neighbours <= 0) return fail(DCI_B200_ERR_ARG, "num_neighbours must be positive, got %d", num_neighbours);
+    DeviceGuard g(h->device);
+    const size_t qbytes = sizeof(float) * (size_t)num_queries * h->dim;
+    const size_t obytes = sizeof(int) * (size_t)num_queries * num_neighbours;
+    DCI_CUDA(h->hq.ensure(qbytes));
+    DCI_CUDA(h->hids.ensure(obytes));
+    DCI_CUDA(h->hdists.ensure(obytes));
+    DCI_CUDA(cudaMemcpyAsync(h->hq.p, h_query, qbytes, cudaMemcpyHostToDevice, 0));
+    int rc = dci_b200_query(h, (const float *)h->hq.p, num_queries, num_neighbours, num_outer_iterations,
+                            max_num_candidates, blind, block_size, thread_size, (int *)h->hids.p,
+                            (float *)h->hdists.p, nullptr);
+    if (rc) return rc;
+    DCI_CUDA(cudaMemcpyAsync(h_ids, h->hids.p, obytes, cudaMemcpyDeviceToHost, 0));
+    DCI_CUDA(cudaMemcpyAsync(h_dists, h->hdists.p, obytes, cudaMemcpyDeviceToHost, 0));
+    DCI_CUDA(cudaStreamSynchronize(0));
+    return 0;
+}
+
+int dci_b200_clear(dci_b200_t *h) {
+    if (int rc = check_handle(h)) return rc;
+    DeviceGuard g(h->device);
+    DCI_CUDA(cudaDeviceSynchronize());
+    h->keys.release(); h->ids.release(); h->tmp_keys.release();
+    h->num_points = 0; h->d_data = nullptr; h->P = h->T = h->ppb = h->num_parts = 0;
+    return 0;
+}
+
+int dci_b200_reset(dci_b200_t *h, unsigned long long seed) {
+    if (int rc = dci_b200_clear(h)) return rc;
+    DeviceGuard g(h->device);
+    if (int rc = launch_directions(h, seed, 0)) return rc;
+    DCI_CUDA(cudaDeviceSynchronize());
+    return 0;
+}
+
+int dci_b200_num_points(dci_b200_t *h) { return h ? h->num_points : 0; }
+
+int dci_b200_get_index(dci_b200_t *h, float *h_keys, int *h_ids) {
+    if (int rc = check_handle(h)) return rc;
+    if (!h_keys || !h_ids) return fail(DCI_B200_ERR_ARG, "null output pointer");
+    if (h->num_points <= 0) return fail(DCI_B200_ERR_STATE, "the index is empty");
+    DeviceGuard g(h->device);
+    DCI_CUDA(cudaDeviceSynchronize());
+    const size_t n = (size_t)h->L * h->S * h->num_points;
+    DCI_CUDA(cudaMemcpy(h_keys, h->keys.p, n * sizeof(float), cudaMemcpyDeviceToHost));
+    DCI_CUDA(cudaMemcpy(h_ids, h->ids.p, n * sizeof(int), cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int dci_b200_project(dci_b200_t *h, const float *d_x, int n, float *d_out, void *stream) {
+    if (int rc = check_handle(h)) return rc;
+    if (!d_x || !d_out || n < 0) return fail(DCI_B200_ERR_ARG, "bad argument to project");
+    DeviceGuard g(h->device);
+    return launch_project(h, d_x, n, d_out, (cudaStream_t)stream);
+}
+
+int dci_b200_enable_work_stats(dci_b200_t *h, int on) {
+    if (int rc = check_handle(h)) return rc;
+    h->stats_on = on ? 1 : 0;
+    if (!on) h->stats_nq = 0;
+    return 0;
+}
+
+int dci_b200_get_work_stats(dci_b200_t *h, long long *h_out, long long capacity_records) {
+    if (int rc = check_handle(h)) return rc;
+    if (!h_out) return fail(DCI_B200_ERR_ARG, "h_out is null");
+    const long long records = (long long)h->stats_nq * h->P;
+    if (records <= 0) return fail(DCI_B200_ERR_STATE, "no work statistics recorded; enable them before the query");
+    if (capacity_records < records) return fail(DCI_B200_ERR_ARG, "capacity %lld below the %lld records available", capacity_records, records);
+    DeviceGuard g(h->device);
+    DCI_CUDA(cudaDeviceSynchronize());
+    DCI_CUDA(cudaMemcpy(h_out, h->stats.p, sizeof(long long) * 6 * (size_t)records, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+long long dci_b200_launch_count(dci_b200_t *h) { return h ? h->launches : 0; }
+
+int dci_b200_merge_shards(const int *d_ids_in, const float *d_dists_in, int num_shards, int num_queries,
+                          int k, const long long *id_offsets, long long *d_ids_out, float *d_dists_out,
+                          int device, void *stream) {
+    if (!d_ids_in || !d_dists_in || !id_offsets || !d_ids_out || !d_dists_out)
+        return fail(DCI_B200_ERR_ARG, "null pointer passed to merge_shards");
+    if (num_shards <= 0 || num_shards > 64 || num_queries < 0 || k <= 0)
+        return fail(DCI_B200_ERR_ARG, "merge_shards needs 1..64 shards, num_queries >= 0 and k > 0");
+    if (k > dci::kMaxTopK) return fail(DCI_B200_ERR_UNSUPPORTED, "k above %d is not supported yet", dci::kMaxTopK);
+    if (num_queries == 0) return 0;
+    for (int s = 0; s < num_shards; ++s)
+        if (id_offsets[s] < 0 || id_offsets[s] > 0x7FFFFFFFll)
+            return fail(DCI_B200_ERR_UNSUPPORTED, "id offsets must lie in [0, 2^31)");
+    DeviceGuard g(device);
+    if (!g.ok) return fail(DCI_B200_ERR_CUDA, "cannot select device %d", device);
+    cudaStream_t st = (cudaStream_t)stream;
+    dci::ShardOffsets off;
+    memset(&off, 0, sizeof(off));
+    for (int s = 0; s < num_shards; ++s) off.v[s] = id_offsets[s];
+    const int threads = 256, cap = next_pow2(k + threads);
+    dci::merge_shards_kernel<<<num_queries, threads, (size_t)cap * 8, st>>>(
+        d_ids_in, d_dists_in, num_shards, num_queries, k, cap, off, d_ids_out, d_dists_out);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(DCI_B200_ERR_CUDA, "merge_shards launch: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+}  // extern "C"

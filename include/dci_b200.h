@@ -1,0 +1,147 @@
+/*
+ * dci_b200.h -- C ABI of the B200-native Prioritized DCI k-NN engine.
+ *
+ * This is the boundary a host binding loads (ctypes, cgo, JNI, a PyTorch
+ * extension ...).  It replaces, function for function, the C API of the
+ * reference project (include/dci.h:58-84) and the pybind entry points built on
+ * it (src/dci_cuda.cpp:175-183).  Differences from that API, all deliberate:
+ *   - extern "C", opaque handle, every call returns a status (0 = ok) and
+ *     dci_b200_last_error() describes the last failure of the calling thread
+ *     (the reference returns void and checks no CUDA error);
+ *   - the caller allocates the outputs (the reference cudaMallocs them and
+ *     never frees them, src/dci_cuda.cpp:100-101);
+ *   - work is enqueued on the stream the caller passes (the reference uses the
+ *     legacy default stream and synchronises the device after every kernel);
+ *   - projection directions can be read and written, and the generator takes
+ *     an explicit seed (the reference seeds cuRAND from the process-global
+ *     rand(), src/util_kernel.cu:124-127).
+ *
+ * All pointers named d_* are device pointers on the handle's device; h_* are
+ * host pointers.  `stream` is a cudaStream_t passed as void* (NULL = default
+ * stream).  Unless stated otherwise calls are asynchronous with respect to the
+ * host: results are complete when the stream reaches the end of the enqueued
+ * work.
+ */
+#ifndef DCI_B200_H
+#define DCI_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct dci_b200 dci_b200_t;
+
+enum {
+    DCI_B200_OK = 0,
+    DCI_B200_ERR_ARG = 1,        /* bad argument (message says which)          */
+    DCI_B200_ERR_STATE = 2,      /* e.g. add() on a non-empty index            */
+    DCI_B200_ERR_CUDA = 3,       /* a CUDA call failed                         */
+    DCI_B200_ERR_UNSUPPORTED = 4 /* e.g. blind querying                        */
+};
+
+/* Message for the last non-zero status returned to this thread. */
+const char *dci_b200_last_error(void);
+
+/* Version of this ABI (increases when a signature changes). */
+int dci_b200_abi_version(void);
+
+/* Replaces dci_init (include/dci.h:61-62, src/dci_cuda_kernel.cu:93-110) and
+ * _dci_new (src/dci_cuda.cpp:54-66): creates an empty index for `dim`-
+ * dimensional points with L = num_comp_indices composite indices of
+ * S = num_simp_indices simple indices each, on CUDA device `device`, and
+ * generates L*S Gaussian unit directions from `seed` on the device
+ * (replaces dci_gen_proj_vec, src/dci_cuda_kernel.cu:77-90).  Synchronous. */
+int dci_b200_create(dci_b200_t **out, int dim, int num_comp_indices, int num_simp_indices,
+                    int device, unsigned long long seed);
+
+/* Replaces dci_free (include/dci.h:82) and _dci_free.  Synchronous. */
+int dci_b200_destroy(dci_b200_t *h);
+
+/* Directions, row-major [L*S][dim], row i = h + m*S for simple index h of
+ * composite index m (same layout as the reference's proj_vec, include/dci.h:45).
+ * The reference has no such accessors; parity tests need them.  Synchronous.
+ * set_proj is rejected while the index holds points. */
+int dci_b200_get_proj(dci_b200_t *h, float *h_out);
+int dci_b200_set_proj(dci_b200_t *h, const float *h_in);
+
+/* Replaces dci_add (include/dci.h:68-69, src/dci_cuda_kernel.cu:149-187) and
+ * _dci_add: projects the num_points rows of d_data ([num_points][dim] fp32,
+ * row-major) on every direction and sorts each (simple index, partition)
+ * segment by (key, id).  block_size = number of partitions P (each partition
+ * is the id range [b*ppb, (b+1)*ppb), ppb = ceil(num_points / P));
+ * thread_size = the window width T used by queries.  Both are semantic
+ * parameters in the reference (src/dci_cuda_kernel.cu:178, :424-427, :487).
+ * As in the reference the index BORROWS d_data: it must stay valid and
+ * unchanged until clear/reset/destroy.  A second add without clear fails with
+ * DCI_B200_ERR_STATE (dciknn_cuda/core.py:70-71). */
+int dci_b200_add(dci_b200_t *h, const float *d_data, int num_points, int block_size,
+                 int thread_size, void *stream);
+
+/* Replaces dci_query (include/dci.h:71-75, src/dci_cuda_kernel.cu:777-875) and
+ * _dci_query: for each of the num_queries rows of d_query returns the
+ * num_neighbours candidates nearest in Euclidean distance among the points the
+ * prioritized traversal promotes, rows ascending by (distance, id).
+ * num_outer_iterations / max_num_candidates are the fields of
+ * dci_query_config (include/dci.h:52-56) and stop each partition's traversal
+ * exactly as the reference does (src/dci_cuda_kernel.cu:598-607).
+ * block_size / thread_size must equal the values given to add (the reference
+ * passes them on every call).  blind != 0 returns DCI_B200_ERR_UNSUPPORTED
+ * (the reference's blind path writes out of bounds).
+ * d_ids: [num_queries][num_neighbours] int32, d_dists: same shape fp32.  Slots
+ * beyond the number of promoted points hold id -1 and distance +inf. */
+int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
+                   int num_outer_iterations, int max_num_candidates, int blind,
+                   int block_size, int thread_size, int *d_ids, float *d_dists, void *stream);
+
+/* Same query with HOST buffers: copies the queries to the device, runs the
+ * query and copies ids and distances back.  Synchronous. */
+int dci_b200_query_host(dci_b200_t *h, const float *h_query, int num_queries, int num_neighbours,
+                        int num_outer_iterations, int max_num_candidates, int blind,
+                        int block_size, int thread_size, int *h_ids, float *h_dists);
+
+/* Replace dci_clear / dci_reset (include/dci.h:77-80, src/dci_cuda_kernel.cu:
+ * 878-891): clear drops the indexed points and keeps the directions; reset also
+ * draws new directions from `seed`.  Synchronous. */
+int dci_b200_clear(dci_b200_t *h);
+int dci_b200_reset(dci_b200_t *h, unsigned long long seed);
+
+/* Number of points currently indexed. */
+int dci_b200_num_points(dci_b200_t *h);
+
+/* Copies the built index to the host as keys[L*S][N] and ids[L*S][N] (each
+ * partition's segment ascending by (key, id)); the counterpart of reading the
+ * reference's `indices` array (include/dci.h:44).  For tests.  Synchronous. */
+int dci_b200_get_index(dci_b200_t *h, float *h_keys, int *h_ids);
+
+/* Projects n rows of d_x on the handle's directions with the library's exact
+ * fp32 path: d_out[i][p] = <proj[i], x[p]>, layout [L*S][n].  For tests. */
+int dci_b200_project(dci_b200_t *h, const float *d_x, int n, float *d_out, void *stream);
+
+/* When enabled (on != 0), every later query also records, per (query,
+ * partition) work item, what the reference's loop would have done:
+ * [0] the outer iteration it stops at, [1] windows visited, [2] index entries
+ * looked at, [3] points promoted, [4] promotions in lane 0, [5] 1 if every
+ * window of the partition was visited.  get_work_stats copies the records of
+ * the last query to the host as [num_queries][P][6] int64.  Synchronous. */
+int dci_b200_enable_work_stats(dci_b200_t *h, int on);
+int dci_b200_get_work_stats(dci_b200_t *h, long long *h_out, long long capacity_records);
+
+/* Number of kernels this library launched on behalf of this handle so far. */
+long long dci_b200_launch_count(dci_b200_t *h);
+
+/* Replaces the merge of MDCI.query (dciknn_cuda/core.py:146-157): merges D
+ * per-shard result lists, each [num_queries][k] ascending, into the k smallest
+ * per query.  d_ids_in / d_dists_in are [D][num_queries][k] on the current
+ * device; id_offsets[s] (host array) is added to the ids of shard s (the
+ * reference adds data_per_device * s, core.py:149); ties go to the lower
+ * global id, which for sorted shard lists equals the reference's stable sort
+ * of the shard-ordered concatenation.  Negative ids (empty slots) stay -1.
+ * d_ids_out: [num_queries][k] int64; d_dists_out: [num_queries][k] fp32. */
+int dci_b200_merge_shards(const int *d_ids_in, const float *d_dists_in, int num_shards,
+                          int num_queries, int k, const long long *id_offsets,
+                          long long *d_ids_out, float *d_dists_out, int device, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DCI_B200_H */

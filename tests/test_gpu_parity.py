@@ -1,0 +1,177 @@
+"""GPU parity: every stage of the CUDA path against the CPU oracle, through the
+public classes (which call the C ABI).  Integer results (index ids, neighbour
+ids, traversal counters) must be identical; keys and distances are fp32 with a
+fixed summation order on both sides, so they must be bit-identical too."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+
+
+def _dci(c, **kw):
+    from dciknn_cuda_b200 import DCI
+    return DCI(c["data"].shape[1], c["L"], c["S"], c["P"], c["T"], 0, proj=torch.from_numpy(c["proj"]), **kw)
+
+
+def _run_both(c, stats=True):
+    dev = torch.device("cuda", 0)
+    data = torch.from_numpy(c["data"]).to(dev)
+    query = torch.from_numpy(c["query"]).to(dev)
+    g = _dci(c)
+    g.add(data)
+    if stats:
+        g.enable_work_stats(True)
+    mc = c.get("max_cand")
+    ids, dists = g.query(query, c["k"], c["outer"], max_num_candidates=mc, return_int_ids=True)
+    torch.cuda.synchronize()
+    o = oracle.OracleDCI(c["data"].shape[1], c["L"], c["S"], c["P"], c["T"], c["proj"])
+    o.add(c["data"])
+    oi, od, ostats = o.query(c["query"], c["k"], c["outer"], mc, want_stats=True)
+    gstats = g.get_work_stats(query.shape[0]).numpy() if stats else None
+    return g, o, ids.cpu().numpy(), dists.cpu().numpy(), oi, od, gstats, ostats
+
+
+def _assert_same(ids, dists, oi, od, gstats, ostats, name=""):
+    assert np.array_equal(ids, oi), "%s: neighbour ids differ in %d of %d rows" % (
+        name, int((ids != oi).any(1).sum()), ids.shape[0])
+    assert np.array_equal(dists.view(np.uint32), od.view(np.uint32)), "%s: distances not bit-identical" % name
+    if gstats is not None:
+        for col, what in ((1, "windows"), (2, "entries"), (3, "promoted"), (4, "lane-0 promotions"), (5, "exhausted")):
+            assert np.array_equal(gstats[:, :, col], ostats[:, :, col]), "%s: %s differ" % (name, what)
+        live = ostats[:, :, 5] == 0
+        assert np.array_equal(gstats[:, :, 0][live], ostats[:, :, 0][live]), "%s: stop iteration differs" % name
+
+
+def test_directions_unit_norm_and_seeded():
+    from dciknn_cuda_b200 import DCI
+    a = DCI(100, 2, 7, seed=123).get_proj()
+    b = DCI(100, 2, 7, seed=123).get_proj()
+    c = DCI(100, 2, 7, seed=124).get_proj()
+    assert a.shape == (14, 100)
+    assert torch.equal(a, b) and not torch.equal(a, c)
+    assert torch.allclose(a.norm(dim=1), torch.ones(14), atol=1e-6)
+    big = DCI(4096, 4, 16, seed=5).get_proj() * (4096 ** 0.5)      # entries ~ N(0, 1)
+    assert abs(float(big.mean())) < 0.01 and abs(float(big.std()) - 1.0) < 0.01
+    assert abs(float((big ** 4).mean()) - 3.0) < 0.1              # Gaussian kurtosis
+    corr = (big[0] * big[1]).mean()
+    assert abs(float(corr)) < 0.08
+
+
+@pytest.mark.parametrize("n,dim,L,S", [(1000, 100, 2, 7), (777, 37, 3, 12), (5000, 128, 2, 10), (300, 960, 3, 12), (64, 8, 1, 1)])
+def test_projection_bit_exact(n, dim, L, S):
+    from dciknn_cuda_b200 import DCI
+    rng = np.random.default_rng(n)
+    x = rng.standard_normal((n, dim)).astype(np.float32)
+    proj = cases.unit_rows(rng, L * S, dim)
+    g = DCI(dim, L, S, proj=torch.from_numpy(proj))
+    got = g.project(torch.from_numpy(x).cuda()).cpu().numpy()
+    want = oracle.project(proj, x)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("N,P", [(2000, 100), (103, 10), (13, 40), (10000, 1), (30000, 2), (70000, 1), (140000, 2)])
+def test_index_build_matches_oracle(N, P):
+    """Covers the shared-memory sort (u16 and u32 payloads) and the global-scratch sort."""
+    from dciknn_cuda_b200 import DCI
+    rng = np.random.default_rng(N + P)
+    dim, L, S = 16, 2, 3
+    data = rng.standard_normal((N, dim)).astype(np.float32)
+    if N == 2000:
+        data = np.round(data * 2) / 2        # duplicate keys: ties must be ordered by id
+    proj = cases.unit_rows(rng, L * S, dim)
+    g = DCI(dim, L, S, P, 10, proj=torch.from_numpy(proj))
+    g.add(torch.from_numpy(data).cuda())
+    keys, ids = g.get_index()
+    okeys, oids = oracle.build(oracle.project(proj, data), P)
+    assert np.array_equal(ids.numpy(), oids)
+    assert np.array_equal(keys.numpy().view(np.uint32), okeys.view(np.uint32))
+
+
+@pytest.mark.parametrize("row", cases.EDGE_CASES, ids=[r[0] for r in cases.EDGE_CASES])
+def test_query_edge_cases(row):
+    c = cases.edge_case(row)
+    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
+    _assert_same(ids, dists, oi, od, gs, os_, c["name"])
+
+
+def test_example_configuration_is_exact_knn():
+    """configs[0]: exhaustive under the reference's stop rule, so the result is exact k-NN."""
+    c = cases.example_config()
+    c["max_cand"] = None
+    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
+    _assert_same(ids, dists, oi, od, gs, os_, "example")
+    bi, bd = oracle.bruteforce(c["data"], c["query"], c["k"])
+    assert np.array_equal(ids, bi) and np.array_equal(dists.view(np.uint32), bd.view(np.uint32))
+
+
+def test_c2_shaped_partitions():
+    """configs[1] cut down to 4 partitions of 10 000 points (shared-memory path, u16 ranks)."""
+    c = cases.c2_shaped()
+    c["max_cand"] = None
+    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
+    _assert_same(ids, dists, oi, od, gs, os_, "c2-shaped")
+    assert (os_[:, :, 5] == 0).all()          # the quota stops every partition before it runs out
+
+
+def test_large_partition_global_scratch_path():
+    """One partition of 30 000 points does not fit shared memory: global-scratch variant."""
+    rng = np.random.default_rng(3)
+    c = dict(data=cases.latent_linear(rng, 30000, 16, 32, 0.01), query=cases.latent_linear(rng, 6, 16, 32, 0.01),
+             L=2, S=4, P=1, T=10, k=10, outer=5000, max_cand=None, proj=cases.unit_rows(rng, 8, 32))
+    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
+    _assert_same(ids, dists, oi, od, gs, os_, "global-scratch")
+
+
+def test_wide_rank_path():
+    """More than 65 535 windows per composite index: 32-bit ranks."""
+    rng = np.random.default_rng(4)
+    c = dict(data=cases.latent_linear(rng, 20000, 8, 16, 0.01), query=cases.latent_linear(rng, 4, 8, 16, 0.01),
+             L=1, S=4, P=1, T=1, k=5, outer=5000, max_cand=None, proj=cases.unit_rows(rng, 4, 16))
+    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
+    _assert_same(ids, dists, oi, od, gs, os_, "wide-rank")
+
+
+def test_query_host_buffers_match_device_buffers():
+    c = cases.example_config(n=1000, nq=40)
+    g = _dci(c)
+    g.add(torch.from_numpy(c["data"]).cuda())
+    ids, dists = g.query(torch.from_numpy(c["query"]).cuda(), 10, return_int_ids=True)
+    hi, hd = g.query_host(torch.from_numpy(c["query"]), 10)
+    assert torch.equal(ids.cpu(), hi) and torch.equal(dists.cpu(), hd)
+
+
+def test_query_batches_and_repeat_calls_agree():
+    c = cases.example_config(n=1500, nq=64)
+    g = _dci(c)
+    g.add(torch.from_numpy(c["data"]).cuda())
+    q = torch.from_numpy(c["query"]).cuda()
+    a = g.query(q, 10)
+    b = g.query(q, 10)
+    one = g.query(q[5], 10)
+    assert a[0].dtype == torch.float32 and a[0].shape == (64, 10)
+    assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])
+    assert torch.equal(one[0][0], a[0][5]) and torch.equal(one[1][0], a[1][5])
+    assert g.launch_count() > 0
+
+
+def test_mdci_two_shards_on_one_device_matches_oracle():
+    """MDCI's sharding and merge (reference core.py:121-157) with both shards on GPU 0."""
+    from dciknn_cuda_b200 import MDCI
+    rng = np.random.default_rng(11)
+    data = cases.latent_linear(rng, 3001, 20, 48)
+    query = cases.latent_linear(rng, 33, 20, 48)
+    projs = [cases.unit_rows(rng, 10, 48) for _ in range(3)]
+    m = MDCI(48, 2, 5, 20, 10, devices=[0, 0, 0], projs=[torch.from_numpy(p) for p in projs])
+    m.add(torch.from_numpy(data))
+    ids, dists = m.query(torch.from_numpy(query).cuda(), 10, return_int_ids=True)
+    o = oracle.OracleMDCI(48, 2, 5, 20, 10, projs)
+    o.add(data)
+    oi, od = o.query(query, 10)
+    assert np.array_equal(ids.cpu().numpy(), oi)
+    assert np.array_equal(dists.cpu().numpy().view(np.uint32), od.view(np.uint32))
+    f_ids, _ = m.query(torch.from_numpy(query).cuda(), 10)
+    assert f_ids.dtype == torch.float32 and torch.equal(f_ids.long(), ids)
