@@ -29,7 +29,8 @@ def _default_seed():
     # a fresh stream of directions per instance, like the reference, where every
     # _dci_new advances rand(); deterministic per process unless DCI_B200_SEED moves it
     base = int(os.environ.get("DCI_B200_SEED", "0"))
-    return (base * 0x9E3779B97F4A7C15 + next(_seed_counter)) & 0xFFFFFFFFFFFFFFFF
+    z = (base * 0x9E3779B97F4A7C15 + next(_seed_counter) * 0xBF58476D1CE4E5B9 + 0x94D049BB133111EB) & 0xFFFFFFFFFFFFFFFF
+    return z ^ (z >> 31)
 
 
 def _device_index(device):
@@ -235,6 +236,15 @@ class DCI(object):
         _capi.check(_capi.lib().dci_b200_get_work_stats(self._live(), C.c_void_p(out.data_ptr()),
                                                        num_queries * self._block_size))
         return out
+
+    def enable_timing(self, on=True):
+        _capi.check(_capi.lib().dci_b200_enable_timing(self._live(), 1 if on else 0))
+
+    def get_timing(self):
+        """dict of milliseconds spent by the last query per kernel group (timing must be enabled)."""
+        buf = (C.c_float * 4)()
+        _capi.check(_capi.lib().dci_b200_get_timing(self._live(), buf))
+        return dict(project_ms=buf[0], traverse_ms=buf[1], merge_ms=buf[2], traverse_launches=int(buf[3]))
 
     def launch_count(self):
         return int(_capi.lib().dci_b200_launch_count(self._live()))

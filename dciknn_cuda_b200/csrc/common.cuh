@@ -196,7 +196,9 @@ struct CtaTopK {
         __syncthreads();
     }
     __device__ __forceinline__ void offer(uint64_t key) {
-        if (*count > cap - (int)blockDim.x) compact();     // uniform: count is shared
+        const int c = *count;      // read by every thread before any thread of this round appends
+        __syncthreads();
+        if (c > cap - (int)blockDim.x) compact();
         if (key < *thresh) {
             const int slot = atomicAdd(count, 1);
             buf[slot] = key;

@@ -75,6 +75,10 @@ struct dci_b200 {
     Buf keys, ids;                       // [L*S][N] sorted index
     Buf tmp_keys, qproj, part_topk, scratch, stats, hq, hids, hdists;
     int stats_on = 0, stats_nq = 0;
+    int timing_on = 0;
+    cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    float t_project = 0.f, t_traverse = 0.f, t_merge = 0.f;
+    int t_traverse_launches = 0;
     long long launches = 0;
     int sm_count = 0;
     size_t smem_optin = 0, smem_per_sm = 0;
@@ -223,6 +227,7 @@ int dci_b200_destroy(dci_b200_t *h) {
                    &h->hq, &h->hids, &h->hdists};
     for (Buf *b : bufs) b->release();
     if (h->d_proj) cudaFree(h->d_proj);
+    for (auto &e : h->ev) if (e) cudaEventDestroy(e);
     delete h;
     return 0;
 }
@@ -301,7 +306,15 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
     cudaStream_t st = (cudaStream_t)stream;
     const int I = h->L * h->S;
     DCI_CUDA(h->qproj.ensure(sizeof(float) * (size_t)I * num_queries));
+    const bool timing = h->timing_on != 0;
+    if (timing) {
+        for (auto &e : h->ev) if (!e) DCI_CUDA(cudaEventCreate(&e));
+        h->t_project = h->t_traverse = h->t_merge = 0.f;
+        h->t_traverse_launches = 0;
+        DCI_CUDA(cudaEventRecord(h->ev[0], st));
+    }
     if (int rc = launch_project(h, d_query, num_queries, (float *)h->qproj.p, st)) return rc;
+    if (timing) DCI_CUDA(cudaEventRecord(h->ev[1], st));
 
     dci::TraverseParams prm;
     memset(&prm, 0, sizeof(prm));
@@ -335,13 +348,24 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
     for (int q0 = 0; q0 < num_queries; q0 += batch) {
         prm.q0 = q0;
         prm.nq = std::min(batch, num_queries - q0);
+        if (timing) DCI_CUDA(cudaEventRecord(h->ev[2], st));
         int rc = (prm.wcap <= 65535) ? launch_traverse<uint16_t>(h, prm, nthreads, st)
                                      : launch_traverse<uint32_t>(h, prm, nthreads, st);
         if (rc) return rc;
+        if (timing) DCI_CUDA(cudaEventRecord(h->ev[3], st));
         dci::merge_partitions_kernel<<<prm.nq, merge_threads, (size_t)merge_cap * 8, st>>>(
             prm.part_topk, h->num_parts, num_neighbours, merge_cap, q0, d_ids, d_dists);
         h->launches++;
         DCI_CUDA(cudaGetLastError());
+        if (timing) {   // timing mode synchronises after every batch; it is off by default
+            float ms = 0.f;
+            DCI_CUDA(cudaEventRecord(h->ev[4], st));
+            DCI_CUDA(cudaEventSynchronize(h->ev[4]));
+            if (q0 == 0) { DCI_CUDA(cudaEventElapsedTime(&ms, h->ev[0], h->ev[1])); h->t_project = ms; }
+            DCI_CUDA(cudaEventElapsedTime(&ms, h->ev[2], h->ev[3])); h->t_traverse += ms;
+            DCI_CUDA(cudaEventElapsedTime(&ms, h->ev[3], h->ev[4])); h->t_merge += ms;
+            h->t_traverse_launches++;
+        }
     }
     return 0;
 }
@@ -429,6 +453,20 @@ int dci_b200_get_work_stats(dci_b200_t *h, long long *h_out, long long capacity_
 }
 
 long long dci_b200_launch_count(dci_b200_t *h) { return h ? h->launches : 0; }
+
+int dci_b200_enable_timing(dci_b200_t *h, int on) {
+    if (int rc = check_handle(h)) return rc;
+    h->timing_on = on ? 1 : 0;
+    return 0;
+}
+
+int dci_b200_get_timing(dci_b200_t *h, float *h_ms) {
+    if (int rc = check_handle(h)) return rc;
+    if (!h_ms) return fail(DCI_B200_ERR_ARG, "h_ms is null");
+    h_ms[0] = h->t_project; h_ms[1] = h->t_traverse; h_ms[2] = h->t_merge;
+    h_ms[3] = (float)h->t_traverse_launches;
+    return 0;
+}
 
 int dci_b200_merge_shards(const int *d_ids_in, const float *d_dists_in, int num_shards, int num_queries,
                           int k, const long long *id_offsets, long long *d_ids_out, float *d_dists_out,

@@ -129,6 +129,15 @@ int dci_b200_get_work_stats(dci_b200_t *h, long long *h_out, long long capacity_
 /* Number of kernels this library launched on behalf of this handle so far. */
 long long dci_b200_launch_count(dci_b200_t *h);
 
+/* When enabled, every later query brackets its kernels with CUDA events on the
+ * caller's stream and synchronises after each batch (so it is for measurement,
+ * not production).  get_timing returns, for the last query, milliseconds spent
+ * in [0] query projection, [1] the traversal kernel (all launches), [2] the
+ * partition merge, and [3] the number of traversal launches.  The reference
+ * has no timers (example.py:74-84 prints wall-clock deltas). */
+int dci_b200_enable_timing(dci_b200_t *h, int on);
+int dci_b200_get_timing(dci_b200_t *h, float *h_ms);
+
 /* Replaces the merge of MDCI.query (dciknn_cuda/core.py:146-157): merges D
  * per-shard result lists, each [num_queries][k] ascending, into the k smallest
  * per query.  d_ids_in / d_dists_in are [D][num_queries][k] on the current

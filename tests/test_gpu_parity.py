@@ -35,7 +35,15 @@ def _run_both(c, stats=True):
     return g, o, ids.cpu().numpy(), dists.cpu().numpy(), oi, od, gstats, ostats
 
 
-def _assert_same(ids, dists, oi, od, gstats, ostats, name=""):
+def _limits(c):
+    """n * S * T per partition: the reference's loop bound (dci_cuda_kernel.cu:458)."""
+    N, P = c["data"].shape[0], c["P"]
+    ppb = -(-N // P)
+    n = np.clip(N - ppb * np.arange(P), 0, ppb)
+    return n * c["S"] * c["T"]
+
+
+def _assert_same(ids, dists, oi, od, gstats, ostats, name="", limits=None):
     assert np.array_equal(ids, oi), "%s: neighbour ids differ in %d of %d rows" % (
         name, int((ids != oi).any(1).sum()), ids.shape[0])
     assert np.array_equal(dists.view(np.uint32), od.view(np.uint32)), "%s: distances not bit-identical" % name
@@ -43,6 +51,8 @@ def _assert_same(ids, dists, oi, od, gstats, ostats, name=""):
         for col, what in ((1, "windows"), (2, "entries"), (3, "promoted"), (4, "lane-0 promotions"), (5, "exhausted")):
             assert np.array_equal(gstats[:, :, col], ostats[:, :, col]), "%s: %s differ" % (name, what)
         live = ostats[:, :, 5] == 0
+        if limits is not None:      # a loop that ran into its bound reports the bound itself
+            live &= ostats[:, :, 0] < limits[None, :]
         assert np.array_equal(gstats[:, :, 0][live], ostats[:, :, 0][live]), "%s: stop iteration differs" % name
 
 
@@ -95,7 +105,7 @@ def test_index_build_matches_oracle(N, P):
 def test_query_edge_cases(row):
     c = cases.edge_case(row)
     _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
-    _assert_same(ids, dists, oi, od, gs, os_, c["name"])
+    _assert_same(ids, dists, oi, od, gs, os_, c["name"], _limits(c))
 
 
 def test_example_configuration_is_exact_knn():
