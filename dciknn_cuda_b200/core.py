@@ -329,6 +329,15 @@ class MDCI(object):
                 shard = shard.to(eng.device).contiguous()
             eng.add(shard)
 
+    def add_local(self, shard, data_per_device):
+        """process_group mode only: index `shard` (this rank's rows, already cut by
+        the caller) and use `data_per_device` as the id stride between ranks, as
+        add() would after slicing a full tensor."""
+        if self._pg is None:
+            raise RuntimeError("add_local needs MDCI(process_group=...)")
+        self.data_per_device = int(data_per_device)
+        self.dcis[0].add(shard)
+
     def query(self, query, num_neighbours=-1, num_outer_iterations=5000, blind=False, *,
               max_num_candidates=None, return_int_ids=False):
         if num_neighbours <= 0:
