@@ -229,6 +229,10 @@ def bench_ours(args):
     out = None
     if rank == 0:
         # roofline of the dominant kernel (traversal): algorithmic bytes from the work counters
+        local_dci.enable_work_stats(False, phases=True)
+        local_dci.query(query, cfg["k"], cfg["outer"])
+        torch.cuda.synchronize()
+        phases = local_dci.get_phase_cycles()
         local_dci.enable_work_stats(True)
         local_dci.query(query, cfg["k"], cfg["outer"])
         torch.cuda.synchronize()
@@ -255,7 +259,8 @@ def bench_ours(args):
                     "frac": achieved / peak, "peak_source": "measured" if peaks else "fallback",
                     "traffic": None, "algorithmic_bytes_per_launch": algo_bytes // max(nl, 1),
                     "launch_ms": tr_ms, "project_ms": statistics.mean(pj), "merge_ms": statistics.mean(mg),
-                    "entries_per_query": entries / nq, "candidates_per_query": cands / nq}
+                    "entries_per_query": entries / nq, "candidates_per_query": cands / nq,
+                    "phase_cycles_per_work_item": {k: v / max(phases["work_items"], 1) for k, v in phases.items() if k != "work_items"}}
         nrec = min(1000, nq)
         rec = recall_at_k(ids[:nrec] if world == 1 else ids[:nrec], data, query[:nrec], cfg["k"]) if world == 1 else None
         cpu_port, cpu_brute = (None, None)

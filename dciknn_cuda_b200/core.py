@@ -227,14 +227,25 @@ class DCI(object):
                                                     C.c_void_p(out.data_ptr()), _stream_ptr(self._device)))
         return out
 
-    def enable_work_stats(self, on=True):
-        _capi.check(_capi.lib().dci_b200_enable_work_stats(self._live(), 1 if on else 0))
+    def enable_work_stats(self, on=True, phases=False):
+        """on: per-(query, partition) counters; phases: per-phase SM cycle sums."""
+        _capi.check(_capi.lib().dci_b200_enable_work_stats(self._live(), (1 if on else 0) | (2 if phases else 0)))
 
     def get_work_stats(self, num_queries):
         """[num_queries, P, 6] int64: stop iteration, windows, entries, promoted, lane-0 promotions, exhausted."""
         out = torch.zeros(num_queries, self._block_size, 6, dtype=torch.int64)
         _capi.check(_capi.lib().dci_b200_get_work_stats(self._live(), C.c_void_p(out.data_ptr()),
                                                        num_queries * self._block_size))
+        return out
+
+    def get_phase_cycles(self):
+        """SM cycles per traversal phase summed over the work items of the last query
+        (needs enable_work_stats(..., phases=True))."""
+        buf = (C.c_longlong * 16)()
+        _capi.check(_capi.lib().dci_b200_get_phase_cycles(self._live(), buf))
+        names = ["load_search", "priorities", "ordering", "promotion", "stop_candidates", "distance", "topk"]
+        out = {n: int(buf[i]) for i, n in enumerate(names)}
+        out["work_items"] = int(buf[15])
         return out
 
     def enable_timing(self, on=True):

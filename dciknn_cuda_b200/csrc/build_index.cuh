@@ -1,8 +1,13 @@
 // Index build: one stable radix sort per (simple index, partition) segment.
 // Replaces copy_to_indices + sort_indices (+ the recursive device quicksort)
 // of the reference (src/dci_cuda_kernel.cu:113-146, 190-247).  The result is
-// kept as two flat arrays keys[L*S][N] / ids[L*S][N] (SoA) instead of the
-// reference's array of {key, id} structs (include/dci.h:27-30).
+// kept as flat arrays keys[L*S][N] / ids[L*S][N] (SoA) instead of the
+// reference's array of {key, id} structs (include/dci.h:27-30), plus the
+// inverse permutation pos[N][L*S] (point-major, so that one point's positions
+// are contiguous): pos[p][i] = position of point p inside its partition's
+// sorted segment of simple index i (16-bit when partitions hold fewer than
+// 65 536 points), which lets a query look a point's window up directly instead
+// of scattering over index entries.
 // Equal keys are ordered by id (the input order), which the reference leaves
 // unspecified.
 #pragma once
@@ -29,9 +34,9 @@ template <typename ValT, bool SMEM>
 __global__ void __launch_bounds__(1024)
 build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_indices, int ppb,
                       int num_parts, float *__restrict__ skeys, int *__restrict__ sids,
-                      unsigned char *gscratch, size_t gscratch_per_cta) {
+                      ValT *__restrict__ spos, unsigned char *gscratch, size_t gscratch_per_cta) {
     extern __shared__ __align__(16) unsigned char dyn_smem[];
-    __shared__ uint32_t warp_tot[32];
+    __shared__ uint32_t warp_tot[40];
     const BuildLayout<ValT> lay = BuildLayout<ValT>::make(blockDim.x, ppb);
     ValT *hist = reinterpret_cast<ValT *>(dyn_smem);
     unsigned char *big = SMEM ? dyn_smem + lay.hist_bytes : gscratch + (size_t)blockIdx.x * gscratch_per_cta;
@@ -56,6 +61,7 @@ build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_in
         for (int x = threadIdx.x; x < n; x += blockDim.x) {
             skeys[row + x] = ordered_to_float(kA[x]);
             sids[row + x] = (int)(lo + vA[x]);
+            spos[(size_t)(lo + vA[x]) * num_indices + i] = (ValT)x;
         }
         __syncthreads();
     }

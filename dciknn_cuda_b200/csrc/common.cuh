@@ -48,38 +48,39 @@ struct FastDiv {
     }
 };
 
-// Exclusive scan, in place, of 8 * blockDim.x counters laid out so that thread
-// t owns entries [8t, 8t+8).  warp_tot is a 32-entry shared scratch array.
-// Ends with a barrier.
-template <typename CntT>
-__device__ __forceinline__ void cta_exclusive_scan8(CntT *cnt, uint32_t *warp_tot) {
+// Exclusive scan, in place, of a[0..n) by the whole CTA; also returns the total
+// to every thread.  scratch: 33 shared words.  Ends with a barrier.
+__device__ __forceinline__ uint32_t cta_exclusive_scan_u32(uint32_t *a, int n, uint32_t *scratch) {
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, nw = blockDim.x >> 5;
-    CntT *p = cnt + tid * 8;
-    uint32_t v[8], sum = 0;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { v[j] = p[j]; sum += v[j]; }
+    const int per = (n + blockDim.x - 1) / blockDim.x;
+    const int lo = min(tid * per, n), hi = min(lo + per, n);
+    uint32_t sum = 0;
+    for (int j = lo; j < hi; ++j) sum += a[j];
     uint32_t inc = sum;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-        uint32_t t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
         if (lane >= o) inc += t;
     }
-    if (lane == 31) warp_tot[w] = inc;
+    if (lane == 31) scratch[w] = inc;
     __syncthreads();
     if (w == 0) {
-        uint32_t t = lane < nw ? warp_tot[lane] : 0, i2 = t;
+        const uint32_t t = lane < nw ? scratch[lane] : 0;
+        uint32_t i2 = t;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            uint32_t u = __shfl_up_sync(0xFFFFFFFFu, i2, o);
+            const uint32_t u = __shfl_up_sync(0xFFFFFFFFu, i2, o);
             if (lane >= o) i2 += u;
         }
-        warp_tot[lane] = i2 - t;
+        scratch[lane] = i2 - t;
+        if (lane == 31) scratch[32] = i2;
     }
     __syncthreads();
-    uint32_t base = warp_tot[w] + inc - sum;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { p[j] = (CntT)base; base += v[j]; }
+    uint32_t base = scratch[w] + inc - sum;
+    for (int j = lo; j < hi; ++j) { const uint32_t v = a[j]; a[j] = base; base += v; }
+    const uint32_t total = scratch[32];
     __syncthreads();
+    return total;
 }
 
 // Stable LSD radix sort of W (u32 key, ValT payload) pairs by one CTA, 8 bits
@@ -87,10 +88,11 @@ __device__ __forceinline__ void cta_exclusive_scan8(CntT *cnt, uint32_t *warp_to
 // Input in (kA, vA); (kB, vB) is the ping-pong buffer.  With RANK_OUT the last
 // pass writes rank_out[payload] = final position instead of the sorted pairs;
 // otherwise the sorted pairs end in (kA, vA).
-// hist: 256 * (blockDim.x / 32) counters in shared memory; warp_tot: 32 words.
+// hist: 256 * (blockDim.x / 32) counters in shared memory, laid out [warp][digit]
+// so that the lanes of a warp touch different banks; warp_tot: 33 shared words.
 // Stability: warp w owns the contiguous slice [w*C, (w+1)*C) of the input and
 // walks it in order, 32 keys a round; equal digits inside a round are ranked by
-// lane with match.any; the scan runs digit-major, warp-minor.
+// lane with match.any; offsets are prefix sums in (digit, warp) order.
 template <typename ValT, typename CntT, bool RANK_OUT>
 __device__ void cta_radix_sort(uint32_t *kA, ValT *vA, uint32_t *kB, ValT *vB, int W,
                                CntT *hist, uint32_t *warp_tot, ValT *rank_out) {
@@ -98,8 +100,10 @@ __device__ void cta_radix_sort(uint32_t *kA, ValT *vA, uint32_t *kB, ValT *vB, i
     const int C = (W + nw - 1) / nw;
     const int rounds = (C + 31) >> 5;
     const unsigned lt = lanemask_lt();
+    __shared__ uint32_t digit_base[256];
     uint32_t *kin = kA, *kout = kB;
     ValT *vin = vA, *vout = vB;
+    CntT *myhist = hist + w * 256;
     for (int pass = 0; pass < 4; ++pass) {
         const int shift = pass * 8;
         for (int i = tid; i < 256 * nw; i += blockDim.x) hist[i] = 0;
@@ -110,11 +114,22 @@ __device__ void cta_radix_sort(uint32_t *kA, ValT *vA, uint32_t *kB, ValT *vB, i
             const bool valid = off < C && x < W;
             const uint32_t d = valid ? ((kin[x] >> shift) & 255u) : (256u + lane);
             const unsigned peers = __match_any_sync(0xFFFFFFFFu, d);
-            if (valid && lane == __ffs(peers) - 1) hist[d * nw + w] += (CntT)__popc(peers);
+            if (valid && lane == __ffs(peers) - 1) myhist[d] += (CntT)__popc(peers);
             __syncwarp();
         }
         __syncthreads();
-        cta_exclusive_scan8(hist, warp_tot);
+        // hist[w][d] <- number of keys with digit d in warps before w; digit_base[d] <- total of d
+        if (tid < 256) {
+            uint32_t run = 0;
+            for (int ww = 0; ww < nw; ++ww) {
+                const uint32_t c = hist[ww * 256 + tid];
+                hist[ww * 256 + tid] = (CntT)run;
+                run += c;
+            }
+            digit_base[tid] = run;
+        }
+        __syncthreads();
+        cta_exclusive_scan_u32(digit_base, 256, warp_tot);
         const bool last = RANK_OUT && pass == 3;
         for (int r = 0; r < rounds; ++r) {
             const int off = r * 32 + lane;
@@ -126,17 +141,17 @@ __device__ void cta_radix_sort(uint32_t *kA, ValT *vA, uint32_t *kB, ValT *vB, i
             const uint32_t d = valid ? ((key >> shift) & 255u) : (256u + lane);
             const unsigned peers = __match_any_sync(0xFFFFFFFFu, d);
             uint32_t base = 0;
-            if (valid) base = hist[d * nw + w];
+            if (valid) base = myhist[d];
             __syncwarp();
             if (valid) {
-                const uint32_t dest = base + __popc(peers & lt);
+                const uint32_t dest = digit_base[d] + base + __popc(peers & lt);
                 if (last) {
                     rank_out[val] = (ValT)dest;
                 } else {
                     kout[dest] = key;
                     vout[dest] = val;
                 }
-                if (lane == __ffs(peers) - 1) hist[d * nw + w] = (CntT)(base + __popc(peers));
+                if (lane == __ffs(peers) - 1) myhist[d] = (CntT)(base + __popc(peers));
             }
             __syncwarp();
         }
@@ -144,6 +159,99 @@ __device__ void cta_radix_sort(uint32_t *kA, ValT *vA, uint32_t *kB, ValT *vB, i
         uint32_t *tk = kin; kin = kout; kout = tk;
         ValT *tv = vin; vin = vout; vout = tv;
     }
+}
+
+constexpr int kMaxBucket = 48;   // largest bucket the counting rank accepts
+
+// Bucket of a non-negative fp32 key: equal-width value buckets, a monotone map.
+__device__ __forceinline__ int bucket_of(uint32_t key_bits, float scale, int last) {
+    return min(last, (int)(__uint_as_float(key_bits) * scale));
+}
+
+// Second half of the counting rank.  Precondition: every key w in [0, W) has
+// been dropped into bucket_of(key[w]) with slot[w] = its arrival number there
+// and cnt[b] = the size of bucket b (all <= kMaxBucket), cnt[nbuckets] = 0.
+// Moves the keys bucket by bucket into (bkey, bval), then gives every key its
+// rank in ascending (key, tie order): rank = start of its bucket + number of
+// smaller keys inside the bucket.  tie_less(a, b) orders two key indices whose
+// keys are equal.  rank_out[w] receives the rank.  Ends with a barrier.
+template <typename ValT, typename TieLess>
+__device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, int W, const uint8_t *slot,
+                                                          uint32_t *bkey, ValT *bval, uint32_t *cnt,
+                                                          int nbuckets, float scale, uint32_t *scratch,
+                                                          ValT *rank_out, TieLess tie_less) {
+    const int tid = threadIdx.x, last = nbuckets - 1;
+    cta_exclusive_scan_u32(cnt, nbuckets + 1, scratch);      // cnt[b] = start of bucket b, cnt[nbuckets] = W
+    for (int w = tid; w < W; w += blockDim.x) {
+        const uint32_t k = key[w];
+        const uint32_t pos = cnt[bucket_of(k, scale, last)] + (uint32_t)slot[w];
+        bkey[pos] = k;
+        bval[pos] = (ValT)w;
+    }
+    __syncthreads();
+    for (int pos = tid; pos < W; pos += blockDim.x) {
+        const uint32_t k = bkey[pos];
+        const uint32_t v = (uint32_t)bval[pos];
+        const int b = bucket_of(k, scale, last);
+        const uint32_t lo = cnt[b], hi = cnt[b + 1];
+        uint32_t r = lo;
+        for (uint32_t j = lo; j < hi; ++j) {
+            const uint32_t kj = bkey[j];
+            if (kj < k) ++r;
+            else if (kj == k && j != (uint32_t)pos && tie_less((uint32_t)bval[j], v)) ++r;
+        }
+        rank_out[v] = (ValT)r;
+    }
+    __syncthreads();
+}
+
+// The k1-th and k2-th smallest (1-based) of get(0..cnt), whose values are below
+// 2^bits, by radix selection 8 bits at a time.  Requires 1 <= k <= cnt.
+// sel: 2 x 256 shared counters; res: 4 shared words.  Results in out[0], out[1].
+template <typename Get>
+__device__ __forceinline__ void cta_select2(Get get, int cnt, int k1, int k2, int bits,
+                                            uint32_t (*sel)[256], uint32_t *res, uint32_t out[2]) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    int top = ((bits + 7) / 8) * 8 - 8;
+    if (top < 0) top = 0;
+    if (tid == 0) { res[0] = 0u; res[1] = 0u; res[2] = (uint32_t)k1; res[3] = (uint32_t)k2; }
+    for (int shift = top; shift >= 0; shift -= 8) {
+        for (int i = tid; i < 512; i += blockDim.x) sel[i >> 8][i & 255] = 0u;
+        __syncthreads();
+        const uint32_t p0 = res[0], p1 = res[1];
+        for (int j = tid; j < cnt; j += blockDim.x) {
+            const uint32_t v = get(j), hi = (shift + 8 >= 32) ? 0u : (v >> (shift + 8)), d = (v >> shift) & 255u;
+            if (hi == p0) atomicAdd(&sel[0][d], 1u);
+            if (hi == p1) atomicAdd(&sel[1][d], 1u);
+        }
+        __syncthreads();
+        if (tid < 64) {           // warp 0 resolves the first rank, warp 1 the second
+            const int which = tid >> 5;
+            const uint32_t want = res[2 + which];
+            uint32_t c[8], sum = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { c[j] = sel[which][lane * 8 + j]; sum += c[j]; }
+            uint32_t inc = sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+                if (lane >= o) inc += t;
+            }
+            const unsigned reach = __ballot_sync(0xFFFFFFFFu, inc >= want);
+            const int owner = __ffs(reach) - 1;
+            if (lane == owner) {
+                uint32_t before = inc - sum;
+                int d = 0;
+                while (d < 7 && before + c[d] < want) { before += c[d]; ++d; }
+                res[which] = (res[which] << 8) | (uint32_t)(lane * 8 + d);
+                res[2 + which] = want - before;
+            }
+        }
+        __syncthreads();
+    }
+    out[0] = res[0];
+    out[1] = res[1];
+    __syncthreads();
 }
 
 // In-place ascending bitonic sort of `len` (power of two) u64 keys in shared
@@ -163,28 +271,65 @@ __device__ __forceinline__ void cta_bitonic_sort_u64(uint64_t *a, int len) {
     }
 }
 
-// Streaming top-k of u64 keys (smaller is better) by one CTA.
-//   buf   : shared, cap entries, cap = power of two >= k + blockDim.x
-//   state : shared int[2]: [0] = number of valid entries in buf
-// Usage: topk_init; for each round every thread calls topk_offer with at most
-// one key (or kEmptySlot for none) -- all threads must call it; topk_finish
-// leaves the k smallest, ascending, in buf[0..k) (padded with kEmptySlot).
+// Appends one element per lane with pred set to a shared list with a single
+// atomic per warp; returns the slot (valid where pred).  All lanes must call.
+__device__ __forceinline__ int warp_append_slot(bool pred, int *counter) {
+    const unsigned m = __ballot_sync(0xFFFFFFFFu, pred);
+    int base = 0;
+    if ((threadIdx.x & 31) == 0 && m) base = atomicAdd(counter, __popc(m));
+    base = __shfl_sync(0xFFFFFFFFu, base, 0);
+    return base + __popc(m & lanemask_lt());
+}
+
+// Streaming top-k of u64 keys (smaller is better; high word = fp32 distance
+// bits, low word = id) by one CTA.
+//   bufs   : shared, 2 * cap entries (two halves that swap roles),
+//            cap = power of two >= k + blockDim.x
+//   shared state: count, thresh, sel[2][256], res[4] supplied by the caller
+// Usage: init; every round all threads call offer with at most one key each
+// (kEmptySlot for none); finish leaves the k smallest, ascending, in
+// result()[0..k) (padded with kEmptySlot).
+// When the buffer fills up it is reduced to the k smallest: the k-th smallest
+// distance is found by radix selection, the few keys not above it are moved to
+// the other half and only those are sorted.
 struct CtaTopK {
-    uint64_t *buf;
+    uint64_t *buf, *other;
     int *count;
     uint64_t *thresh;   // shared: keys >= *thresh cannot enter the top k
+    uint32_t (*sel)[256];
+    uint32_t *res;
     int cap, k;
 
-    __device__ __forceinline__ void init(uint64_t *b, int *cnt, uint64_t *th, int cap_, int k_) {
-        buf = b; count = cnt; thresh = th; cap = cap_; k = k_;
+    __device__ __forceinline__ void init(uint64_t *bufs, int *cnt, uint64_t *th, uint32_t (*sel_)[256],
+                                         uint32_t *res_, int cap_, int k_) {
+        buf = bufs; other = bufs + cap_; count = cnt; thresh = th; sel = sel_; res = res_; cap = cap_; k = k_;
         if (threadIdx.x == 0) { *count = 0; *thresh = kEmptySlot; }
         __syncthreads();
     }
-    __device__ __forceinline__ void compact() {   // all threads; sorts and keeps k
-        const int c = *count;
+    __device__ __forceinline__ uint64_t *result() { return buf; }
+    __device__ __forceinline__ void compact() {   // all threads; keeps the k smallest, sorted
+        int c = *count;
+        __syncthreads();
+        if (c > k) {
+            uint32_t tau[2];
+            const uint64_t *src = buf;
+            cta_select2([src](int j) { return (uint32_t)(src[j] >> 32); }, c, k, k, 32, sel, res, tau);
+            if (threadIdx.x == 0) *count = 0;
+            __syncthreads();
+            for (int j0 = 0; j0 < c; j0 += blockDim.x) {
+                const int j = j0 + threadIdx.x;
+                const uint64_t key = j < c ? buf[j] : kEmptySlot;
+                const bool take = j < c && (uint32_t)(key >> 32) <= tau[0];
+                const int sl = warp_append_slot(take, count);
+                if (take) other[sl] = key;
+            }
+            __syncthreads();
+            c = *count;
+            uint64_t *t = buf; buf = other; other = t;
+            __syncthreads();
+        }
         int len = 2;
         while (len < c) len <<= 1;
-        __syncthreads();
         for (int i = c + threadIdx.x; i < len; i += blockDim.x) buf[i] = kEmptySlot;
         __syncthreads();
         cta_bitonic_sort_u64(buf, len);
@@ -199,10 +344,9 @@ struct CtaTopK {
         const int c = *count;      // read by every thread before any thread of this round appends
         __syncthreads();
         if (c > cap - (int)blockDim.x) compact();
-        if (key < *thresh) {
-            const int slot = atomicAdd(count, 1);
-            buf[slot] = key;
-        }
+        const bool take = key < *thresh;
+        const int sl = warp_append_slot(take, count);
+        if (take) buf[sl] = key;
         __syncthreads();
     }
     __device__ __forceinline__ void finish() {

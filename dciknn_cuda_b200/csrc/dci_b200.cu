@@ -72,9 +72,9 @@ struct dci_b200 {
     int num_points = 0, P = 0, T = 0, ppb = 0, num_parts = 0;
     const float *d_data = nullptr;       // borrowed
     float *d_proj = nullptr;             // [L*S][dim]
-    Buf keys, ids;                       // [L*S][N] sorted index
-    Buf tmp_keys, qproj, part_topk, scratch, stats, hq, hids, hdists;
-    int stats_on = 0, stats_nq = 0;
+    Buf keys, ids, pos;                  // [L*S][N] sorted index and inverse positions
+    Buf tmp_keys, qproj, part_topk, scratch, stats, phases, hq, hids, hdists;
+    int stats_on = 0, stats_nq = 0, phases_valid = 0;
     int timing_on = 0;
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     float t_project = 0.f, t_traverse = 0.f, t_merge = 0.f;
@@ -123,13 +123,13 @@ int launch_build(dci_b200 *h, const float *d_unsorted, cudaStream_t st) {
         int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + 1024), 2048 / nthreads));
         const unsigned grid = (unsigned)std::min<long long>(nseg, (long long)h->sm_count * per_sm);
         kern<<<grid, nthreads, dyn, st>>>(d_unsorted, h->num_points, I, h->ppb, h->num_parts,
-                                          (float *)h->keys.p, (int *)h->ids.p, nullptr, 0);
+                                          (float *)h->keys.p, (int *)h->ids.p, (ValT *)h->pos.p, nullptr, 0);
     } else {
         auto kern = dci::build_segments_kernel<ValT, false>;
         const unsigned grid = (unsigned)std::min<long long>(nseg, (long long)h->sm_count * (2048 / nthreads));
         DCI_CUDA(h->scratch.ensure(lay.buf_bytes * grid));
         kern<<<grid, nthreads, lay.hist_bytes, st>>>(d_unsorted, h->num_points, I, h->ppb, h->num_parts,
-                                                     (float *)h->keys.p, (int *)h->ids.p,
+                                                     (float *)h->keys.p, (int *)h->ids.p, (ValT *)h->pos.p,
                                                      (unsigned char *)h->scratch.p, lay.buf_bytes);
     }
     h->launches++;
@@ -137,33 +137,32 @@ int launch_build(dci_b200 *h, const float *d_unsorted, cudaStream_t st) {
     return 0;
 }
 
-template <typename ValT>
+template <typename ValT, typename PosT>
 int launch_traverse(dci_b200 *h, dci::TraverseParams prm, int nthreads, cudaStream_t st) {
-    const auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb);
+    auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, true);
     const long long nwork = (long long)prm.nq * prm.num_parts;
     cudaFuncAttributes fa;
-    DCI_CUDA(cudaFuncGetAttributes(&fa, dci::traverse_kernel<ValT, true>));
+    DCI_CUDA(cudaFuncGetAttributes(&fa, dci::traverse_kernel<ValT, PosT, true>));
     const size_t static_smem = fa.sharedSizeBytes;
     if (lay.fixed_bytes + static_smem > h->smem_optin)
         return fail(DCI_B200_ERR_UNSUPPORTED, "dim=%d with k=%d needs %zu bytes of shared memory per CTA, more than the device offers",
                     prm.dim, prm.knn, lay.fixed_bytes + static_smem);
     const bool smem = lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin;
+    if (!smem) lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, false);
+    const size_t dyn = smem ? lay.fixed_bytes + lay.big_bytes : lay.fixed_bytes;
+    const size_t per_cta = lay.fallback_bytes + (smem ? 0 : lay.big_bytes);
+    const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));
+    const unsigned grid = (unsigned)std::min<long long>(nwork, (long long)h->sm_count * per_sm);
+    DCI_CUDA(h->scratch.ensure(per_cta * grid));
+    prm.gscratch = (unsigned char *)h->scratch.p;
+    prm.gscratch_per_cta = per_cta;
     if (smem) {
-        auto kern = dci::traverse_kernel<ValT, true>;
-        const size_t dyn = lay.fixed_bytes + lay.big_bytes;
+        auto kern = dci::traverse_kernel<ValT, PosT, true>;
         DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-        const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));
-        const unsigned grid = (unsigned)std::min<long long>(nwork, (long long)h->sm_count * per_sm);
         kern<<<grid, nthreads, dyn, st>>>(prm);
     } else {
-        auto kern = dci::traverse_kernel<ValT, false>;
-        const size_t dyn = lay.fixed_bytes;
+        auto kern = dci::traverse_kernel<ValT, PosT, false>;
         DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-        const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));
-        const unsigned grid = (unsigned)std::min<long long>(nwork, (long long)h->sm_count * per_sm);
-        DCI_CUDA(h->scratch.ensure(lay.big_bytes * grid));
-        prm.gscratch = (unsigned char *)h->scratch.p;
-        prm.gscratch_per_cta = lay.big_bytes;
         kern<<<grid, nthreads, dyn, st>>>(prm);
     }
     h->launches++;
@@ -223,7 +222,7 @@ int dci_b200_destroy(dci_b200_t *h) {
     if (!h) return 0;
     DeviceGuard g(h->device);
     cudaDeviceSynchronize();
-    Buf *bufs[] = {&h->keys, &h->ids, &h->tmp_keys, &h->qproj, &h->part_topk, &h->scratch, &h->stats,
+    Buf *bufs[] = {&h->keys, &h->ids, &h->pos, &h->tmp_keys, &h->qproj, &h->part_topk, &h->scratch, &h->stats, &h->phases,
                    &h->hq, &h->hids, &h->hdists};
     for (Buf *b : bufs) b->release();
     if (h->d_proj) cudaFree(h->d_proj);
@@ -275,6 +274,7 @@ int dci_b200_add(dci_b200_t *h, const float *d_data, int num_points, int block_s
     const size_t n_entries = (size_t)I * num_points;
     DCI_CUDA(h->keys.ensure(n_entries * sizeof(float)));
     DCI_CUDA(h->ids.ensure(n_entries * sizeof(int)));
+    DCI_CUDA(h->pos.ensure(n_entries * (ppb <= 65535 ? sizeof(uint16_t) : sizeof(uint32_t))));
     DCI_CUDA(h->tmp_keys.ensure(n_entries * sizeof(float)));
     h->num_points = num_points; h->P = block_size; h->T = thread_size; h->ppb = ppb; h->num_parts = num_parts;
     h->d_data = d_data;
@@ -318,7 +318,7 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
 
     dci::TraverseParams prm;
     memset(&prm, 0, sizeof(prm));
-    prm.skeys = (const float *)h->keys.p; prm.sids = (const int *)h->ids.p; prm.data = h->d_data;
+    prm.skeys = (const float *)h->keys.p; prm.sids = (const int *)h->ids.p; prm.spos = h->pos.p; prm.data = h->d_data;
     prm.qproj = (const float *)h->qproj.p; prm.query = d_query;
     prm.N = h->num_points; prm.dim = h->dim; prm.L = h->L; prm.S = h->S; prm.P = h->P; prm.T = h->T;
     prm.ppb = h->ppb; prm.num_parts = h->num_parts; prm.nq_total = num_queries;
@@ -334,7 +334,13 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
     const int merge_threads = 256;
     const int merge_cap = next_pow2(num_neighbours + merge_threads);
 
-    if (h->stats_on) {
+    if (h->stats_on & 2) {
+        DCI_CUDA(h->phases.ensure(sizeof(long long) * 16));
+        DCI_CUDA(cudaMemsetAsync(h->phases.p, 0, sizeof(long long) * 16, st));
+        prm.phase_cycles = (long long *)h->phases.p;
+        h->phases_valid = 1;
+    }
+    if (h->stats_on & 1) {
         const size_t bytes = sizeof(long long) * 6 * (size_t)num_queries * h->P;
         DCI_CUDA(h->stats.ensure(bytes));
         DCI_CUDA(cudaMemsetAsync(h->stats.p, 0, bytes, st));
@@ -349,11 +355,15 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
         prm.q0 = q0;
         prm.nq = std::min(batch, num_queries - q0);
         if (timing) DCI_CUDA(cudaEventRecord(h->ev[2], st));
-        int rc = (prm.wcap <= 65535) ? launch_traverse<uint16_t>(h, prm, nthreads, st)
-                                     : launch_traverse<uint32_t>(h, prm, nthreads, st);
+        int rc;
+        if (prm.ppb <= 65535)
+            rc = (prm.wcap <= 65535) ? launch_traverse<uint16_t, uint16_t>(h, prm, nthreads, st)
+                                     : launch_traverse<uint32_t, uint16_t>(h, prm, nthreads, st);
+        else
+            rc = launch_traverse<uint32_t, uint32_t>(h, prm, nthreads, st);
         if (rc) return rc;
         if (timing) DCI_CUDA(cudaEventRecord(h->ev[3], st));
-        dci::merge_partitions_kernel<<<prm.nq, merge_threads, (size_t)merge_cap * 8, st>>>(
+        dci::merge_partitions_kernel<<<prm.nq, merge_threads, (size_t)merge_cap * 16, st>>>(
             prm.part_topk, h->num_parts, num_neighbours, merge_cap, q0, d_ids, d_dists);
         h->launches++;
         DCI_CUDA(cudaGetLastError());
@@ -399,7 +409,7 @@ int dci_b200_clear(dci_b200_t *h) {
     if (int rc = check_handle(h)) return rc;
     DeviceGuard g(h->device);
     DCI_CUDA(cudaDeviceSynchronize());
-    h->keys.release(); h->ids.release(); h->tmp_keys.release();
+    h->keys.release(); h->ids.release(); h->pos.release(); h->tmp_keys.release();
     h->num_points = 0; h->d_data = nullptr; h->P = h->T = h->ppb = h->num_parts = 0;
     return 0;
 }
@@ -435,8 +445,9 @@ int dci_b200_project(dci_b200_t *h, const float *d_x, int n, float *d_out, void 
 
 int dci_b200_enable_work_stats(dci_b200_t *h, int on) {
     if (int rc = check_handle(h)) return rc;
-    h->stats_on = on ? 1 : 0;
-    if (!on) h->stats_nq = 0;
+    h->stats_on = on & 3;
+    if (!(on & 1)) h->stats_nq = 0;
+    if (!(on & 2)) h->phases_valid = 0;
     return 0;
 }
 
@@ -449,6 +460,16 @@ int dci_b200_get_work_stats(dci_b200_t *h, long long *h_out, long long capacity_
     DeviceGuard g(h->device);
     DCI_CUDA(cudaDeviceSynchronize());
     DCI_CUDA(cudaMemcpy(h_out, h->stats.p, sizeof(long long) * 6 * (size_t)records, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int dci_b200_get_phase_cycles(dci_b200_t *h, long long *h_out) {
+    if (int rc = check_handle(h)) return rc;
+    if (!h_out) return fail(DCI_B200_ERR_ARG, "h_out is null");
+    if (!h->phases.p || !h->phases_valid) return fail(DCI_B200_ERR_STATE, "no work statistics recorded; enable them before the query");
+    DeviceGuard g(h->device);
+    DCI_CUDA(cudaDeviceSynchronize());
+    DCI_CUDA(cudaMemcpy(h_out, h->phases.p, sizeof(long long) * 16, cudaMemcpyDeviceToHost));
     return 0;
 }
 
@@ -487,7 +508,7 @@ int dci_b200_merge_shards(const int *d_ids_in, const float *d_dists_in, int num_
     memset(&off, 0, sizeof(off));
     for (int s = 0; s < num_shards; ++s) off.v[s] = id_offsets[s];
     const int threads = 256, cap = next_pow2(k + threads);
-    dci::merge_shards_kernel<<<num_queries, threads, (size_t)cap * 8, st>>>(
+    dci::merge_shards_kernel<<<num_queries, threads, (size_t)cap * 16, st>>>(
         d_ids_in, d_dists_in, num_shards, num_queries, k, cap, off, d_ids_out, d_dists_out);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(DCI_B200_ERR_CUDA, "merge_shards launch: %s", cudaGetErrorString(e));

@@ -15,14 +15,16 @@
 //   1. finds every simple index's split position with a warp-wide 32-ary search
 //      (replaces dci_search_index, :279-297),
 //   2. enumerates all windows with their priorities (dci_next_closest_proj,
-//      :250-273, and the priority rule :338-352, :572-590) and radix-sorts the
-//      windows of each composite index: the rank of a window IS the outer
-//      iteration in which the reference visits it,
-//   3. for every point takes, per composite index, the largest rank among the
-//      S windows that contain it (= the iteration of its S-th visit, i.e. its
-//      promotion) with the lane it occupies in that window, and then the
-//      smallest such rank over the composite indices (the first promotion wins,
-//      :497),
+//      :250-273, and the priority rule :338-352, :572-590) and ranks the windows
+//      of each composite index in that order (a counting rank over value
+//      buckets; a stable radix sort when many priorities are equal): the rank of
+//      a window IS the outer iteration in which the reference visits it,
+//   3. for every point looks up (through the inverse permutation built by add)
+//      the window that contains it in each simple index and takes, per
+//      composite index, the largest rank among those S windows (= the iteration
+//      of its S-th visit, i.e. its promotion) with the lane it occupies in that
+//      window, and then the smallest such rank over the composite indices (the
+//      first promotion wins, :497),
 //   4. derives the stop iteration from the order statistics of the promotion
 //      iterations of lane-0 points (the reference's stop test), and
 //   5. computes true distances of the points promoted up to the stop iteration
@@ -39,12 +41,14 @@ namespace dci {
 struct TraverseParams {
     const float *skeys;        // [I][N] sorted keys
     const int *sids;           // [I][N] point ids
+    const void *spos;          // [N][I] position of each point in its sorted segments (u16 or u32)
     const float *data;         // [N][dim]
     const float *qproj;        // [I][nq_total]
     const float *query;        // [nq_total][dim]
     uint64_t *part_topk;       // [nq][num_parts][knn]
     long long *work_stats;     // nullptr or [nq_total][P][6]
-    unsigned char *gscratch;   // per-CTA slabs (global-scratch variant)
+    long long *phase_cycles;   // nullptr or [16]: SM cycles summed over work items, per phase
+    unsigned char *gscratch;   // per-CTA slabs
     size_t gscratch_per_cta;
     long long outer_s;         // num_outer_iterations * S
     int N, dim, L, S, P, T, ppb, num_parts;
@@ -57,27 +61,50 @@ struct TraverseParams {
     FastDiv divT;
 };
 
+constexpr int kDistChunk = 16;                 // floats of a row staged per step of the distance phase
+constexpr int kDistStride = kDistChunk + 4;    // padded row stride of the staging tile (floats)
+
 template <typename ValT>
 struct TraverseLayout {
-    // dynamic shared memory, always: [hist][qvec][topk buf]
-    size_t hist_bytes, qvec_bytes, topk_bytes, fixed_bytes;
-    // "big" region (shared or global): [rank tables][union(sort buffers, point arrays)]
-    size_t rank_bytes, sortk_bytes, sortv_bytes, point_bytes, big_bytes;
+    // dynamic shared memory, always: [counters][qvec]
+    size_t cnt_bytes, qvec_bytes, fixed_bytes;
+    int nbuckets;
+    // "big" region (shared or global): [rank table per composite][union]
+    //   union, ordering view : kA u32[wcap] | bkey u32[wcap] | bval ValT[wcap] | slot u8[wcap]
+    //   union, point view    : kenc u32[ppb] | ... | list ValT[ppb] at list_off
+    //   union, distance view : top-k 2 x u64[topk_cap] | staging tiles | ... | list (kept)
+    size_t rank_bytes, wk_bytes, wv_bytes, ws_bytes, point_bytes, list_bytes, topk_bytes, tile_bytes,
+        list_off, big_bytes;
+    // per-CTA global slab for the radix-sort fallback: 2 x u32[wcap] | 2 x ValT[wcap]
+    size_t fallback_bytes;
     __host__ __device__ static size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
     __host__ __device__ static TraverseLayout make(int nthreads, int dim, int topk_cap, int L,
-                                                   int wcap, int ppb) {
+                                                   int wcap, int ppb, bool smem) {
         TraverseLayout l;
-        l.hist_bytes = align16((size_t)256 * (nthreads / 32) * sizeof(ValT));
+        const size_t radix_hist = (size_t)256 * (nthreads / 32) * sizeof(ValT);
+        int nb = wcap / 2;
+        if (nb < 64) nb = 64;
+        if (nb > 8190) nb = 8190;
+        l.nbuckets = nb;
+        const size_t bucket_cnt = (size_t)4 * (nb + 1);
+        l.cnt_bytes = align16(radix_hist > bucket_cnt ? radix_hist : bucket_cnt);
         l.qvec_bytes = align16((size_t)dim * 4);
-        l.topk_bytes = align16((size_t)topk_cap * 8);
-        l.fixed_bytes = l.hist_bytes + l.qvec_bytes + l.topk_bytes;
+        l.fixed_bytes = l.cnt_bytes + l.qvec_bytes;
         l.rank_bytes = align16((size_t)L * wcap * sizeof(ValT));
-        l.sortk_bytes = align16((size_t)wcap * 4);
-        l.sortv_bytes = align16((size_t)wcap * sizeof(ValT));
+        l.wk_bytes = align16((size_t)wcap * 4);
+        l.wv_bytes = align16((size_t)wcap * sizeof(ValT));
+        l.ws_bytes = align16((size_t)wcap);
         l.point_bytes = align16((size_t)ppb * 4);
-        const size_t sort_total = 2 * l.sortk_bytes + 2 * l.sortv_bytes;
-        const size_t point_total = 3 * l.point_bytes;
+        l.list_bytes = align16((size_t)ppb * sizeof(ValT));
+        l.topk_bytes = align16((size_t)topk_cap * 8) * 2;
+        // staging tiles only pay off in shared memory
+        l.tile_bytes = smem ? (size_t)(nthreads / 32) * 32 * kDistStride * 4 : 0;
+        const size_t need = l.topk_bytes + l.tile_bytes;
+        l.list_off = l.point_bytes > need ? l.point_bytes : need;
+        const size_t sort_total = 2 * l.wk_bytes + l.wv_bytes + l.ws_bytes;
+        const size_t point_total = l.list_off + l.list_bytes;
         l.big_bytes = l.rank_bytes + (sort_total > point_total ? sort_total : point_total);
+        l.fallback_bytes = 2 * l.wk_bytes + 2 * l.wv_bytes;
         return l;
     }
 };
@@ -99,21 +126,6 @@ __device__ __forceinline__ int cta_sum(int v, uint32_t *scratch) {
     const int r = (int)scratch[32];
     __syncthreads();
     return r;
-}
-
-// Smallest v in [0, vmax] such that at least `kth` entries of list[0..cnt) are
-// <= v (the kth smallest, 1-based).  Requires 1 <= kth <= cnt.
-__device__ __forceinline__ uint32_t cta_kth_smallest(const uint32_t *list, int cnt, int kth,
-                                                     uint32_t vmax, uint32_t *scratch) {
-    uint32_t lo = 0, hi = vmax;
-    while (lo < hi) {
-        const uint32_t mid = lo + ((hi - lo) >> 1);
-        int c = 0;
-        for (int j = threadIdx.x; j < cnt; j += blockDim.x) c += (list[j] <= mid);
-        c = cta_sum(c, scratch);
-        if (c >= kth) hi = mid; else lo = mid + 1;
-    }
-    return lo;
 }
 
 // Euclidean distance with the reference's summation order
@@ -144,7 +156,70 @@ __device__ __forceinline__ float dist_sequential(const float *__restrict__ row, 
     return __fsqrt_rn(sq);
 }
 
-template <typename ValT, bool SMEM>
+// Same distances for 32 rows at a time by one warp: lane r owns row r.  The
+// rows are read from global memory in 64-byte pieces, four lanes per piece so
+// that every 32-byte sector fetched is used in full, staged through a padded
+// shared tile, and each lane then walks its own row in ascending coordinate
+// order, so the result has exactly the summation order of dist_sequential.
+// Requires dim % 4 == 0 and 16-byte aligned rows.  `row_id` is this lane's row
+// (any valid row for lanes without a candidate).
+__device__ __forceinline__ float dist_rows_tiled(const float *__restrict__ data, long long row_id,
+                                                 const float *qv, int dim, float *tile) {
+    const int lane = threadIdx.x & 31;
+    const int sub = lane & 3, rsel = lane >> 2;            // 4 lanes per 64-byte piece, 8 rows per load
+    const float *src[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const long long rid = __shfl_sync(0xFFFFFFFFu, row_id, rsel + 8 * u);
+        src[u] = data + (size_t)rid * dim + sub * 4;
+    }
+    float4 ld[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+        ld[u] = (sub * 4 < dim) ? __ldg(reinterpret_cast<const float4 *>(src[u])) : make_float4(0.f, 0.f, 0.f, 0.f);
+    float sq = 0.0f;
+    for (int c0 = 0; c0 < dim; c0 += kDistChunk) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            *reinterpret_cast<float4 *>(tile + (rsel + 8 * u) * kDistStride + sub * 4) = ld[u];
+        __syncwarp();
+        const int cn = c0 + kDistChunk;
+        if (cn < dim) {
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (cn + sub * 4 < dim) ld[u] = __ldg(reinterpret_cast<const float4 *>(src[u] + cn));
+        }
+        const float *mine = tile + lane * kDistStride;
+#pragma unroll
+        for (int k4 = 0; k4 < kDistChunk / 4; ++k4) {
+            if (c0 + k4 * 4 < dim) {
+                const float4 a = *reinterpret_cast<const float4 *>(mine + k4 * 4);
+                const float4 b = *reinterpret_cast<const float4 *>(qv + c0 + k4 * 4);
+                float d = __fsub_rn(a.x, b.x); sq = __fmaf_rn(d, d, sq);
+                d = __fsub_rn(a.y, b.y); sq = __fmaf_rn(d, d, sq);
+                d = __fsub_rn(a.z, b.z); sq = __fmaf_rn(d, d, sq);
+                d = __fsub_rn(a.w, b.w); sq = __fmaf_rn(d, d, sq);
+            }
+        }
+        __syncwarp();
+    }
+    return __fsqrt_rn(sq);
+}
+
+// Windows of one simple index are numbered in spatial order: window g covers the
+// sorted positions [g*T - c, g*T - c + T), c = nl*T - s - 1, where s is the last
+// position with key < q and nl the number of windows left of the query; windows
+// g < nl lie left of the query, the others right.  The order in which the
+// reference visits the windows of one index (used only to break ties between
+// equal priorities): left windows from the nearest outwards, then right windows
+// outwards -- except that the single right window that exists when every key is
+// below the query comes first (its signed difference is negative,
+// src/dci_cuda_kernel.cu:264-265).
+__device__ __forceinline__ int window_visit_order(int g, int nl, int sp) {
+    return g >= nl ? (sp ? 0 : g) : (nl - 1 - g + sp);
+}
+
+template <typename ValT, typename PosT, bool SMEM>
 __global__ void __launch_bounds__(1024, 1)
 traverse_kernel(const TraverseParams prm) {
     extern __shared__ __align__(16) unsigned char dyn_smem[];
@@ -152,43 +227,63 @@ traverse_kernel(const TraverseParams prm) {
     __shared__ int s_nl[kMaxIndices];        // number of left windows
     __shared__ int s_cnt[kMaxIndices];       // number of windows
     __shared__ int s_sp[kMaxIndices];        // 1: the only right window precedes the left ones
+    __shared__ int2 s_cb[kMaxIndices];       // x: c (window 0 starts at -c), y: first window id in its composite
     __shared__ float s_qp[kMaxIndices];      // projected query
     __shared__ int s_woff[kMaxIndices + 64]; // per composite: S+1 window offsets
     __shared__ uint32_t s_scratch[40];
+    __shared__ uint32_t s_sel[2][256];
+    __shared__ uint32_t s_res[4];
+    __shared__ uint32_t s_maxpri;
     __shared__ int s_count[2];
     __shared__ uint64_t s_thresh;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     const int L = prm.L, S = prm.S, T = prm.T, I = L * S, N = prm.N, dim = prm.dim;
     const TraverseLayout<ValT> lay =
-        TraverseLayout<ValT>::make(blockDim.x, dim, prm.topk_cap, L, prm.wcap, prm.ppb);
-    ValT *hist = reinterpret_cast<ValT *>(dyn_smem);
-    float *qvec = reinterpret_cast<float *>(dyn_smem + lay.hist_bytes);
-    uint64_t *topk_buf = reinterpret_cast<uint64_t *>(dyn_smem + lay.hist_bytes + lay.qvec_bytes);
-    unsigned char *big = SMEM ? dyn_smem + lay.fixed_bytes
-                              : prm.gscratch + (size_t)blockIdx.x * prm.gscratch_per_cta;
+        TraverseLayout<ValT>::make(blockDim.x, dim, prm.topk_cap, L, prm.wcap, prm.ppb, SMEM);
+    uint32_t *cnt = reinterpret_cast<uint32_t *>(dyn_smem);            // bucket counters / radix histogram
+    float *qvec = reinterpret_cast<float *>(dyn_smem + lay.cnt_bytes);
+    unsigned char *slab = prm.gscratch + (size_t)blockIdx.x * prm.gscratch_per_cta;
+    unsigned char *big = SMEM ? dyn_smem + lay.fixed_bytes : slab + lay.fallback_bytes;
     ValT *rank = reinterpret_cast<ValT *>(big);
     unsigned char *uni = big + lay.rank_bytes;
-    // sort view of the union region
+    // ordering view of the union region
     uint32_t *kA = reinterpret_cast<uint32_t *>(uni);
-    uint32_t *kB = reinterpret_cast<uint32_t *>(uni + lay.sortk_bytes);
-    ValT *vA = reinterpret_cast<ValT *>(uni + 2 * lay.sortk_bytes);
-    ValT *vB = reinterpret_cast<ValT *>(uni + 2 * lay.sortk_bytes + lay.sortv_bytes);
+    uint32_t *bkey = reinterpret_cast<uint32_t *>(uni + lay.wk_bytes);
+    ValT *bval = reinterpret_cast<ValT *>(uni + 2 * lay.wk_bytes);
+    uint8_t *slot = reinterpret_cast<uint8_t *>(uni + 2 * lay.wk_bytes + lay.wv_bytes);
+    // radix-sort fallback buffers (global)
+    uint32_t *fb_k0 = reinterpret_cast<uint32_t *>(slab);
+    uint32_t *fb_k1 = reinterpret_cast<uint32_t *>(slab + lay.wk_bytes);
+    ValT *fb_v0 = reinterpret_cast<ValT *>(slab + 2 * lay.wk_bytes);
+    ValT *fb_v1 = reinterpret_cast<ValT *>(slab + 2 * lay.wk_bytes + lay.wv_bytes);
     // point view of the union region
     uint32_t *kenc = reinterpret_cast<uint32_t *>(uni);                       // best promotion per point
-    uint32_t *mr = reinterpret_cast<uint32_t *>(uni + lay.point_bytes);       // promotion in this composite
-    uint32_t *list = reinterpret_cast<uint32_t *>(uni + 2 * lay.point_bytes); // lane-0 ranks, then candidates
+    ValT *list = reinterpret_cast<ValT *>(uni + lay.list_off);                // lane-0 ranks, then candidates
+    // distance view
+    uint64_t *topk_bufs = reinterpret_cast<uint64_t *>(uni);                  // over kenc, phase 5 only
+    float *tiles = reinterpret_cast<float *>(uni + lay.topk_bytes);           // staging, shared variant only
+    const PosT *spos = reinterpret_cast<const PosT *>(prm.spos);
 
     const uint32_t tmask = (1u << prm.tshift) - 1u;
     const long long nwork = (long long)prm.nq * prm.num_parts;
+    long long t_last = 0;
+#define DCI_PHASE_MARK(slot_)                                                             \
+    if (prm.phase_cycles && tid == 0) {                                                   \
+        const long long now_ = clock64();                                                 \
+        atomicAdd((unsigned long long *)&prm.phase_cycles[slot_], (unsigned long long)(now_ - t_last)); \
+        t_last = now_;                                                                    \
+    }
 
     for (long long wi = blockIdx.x; wi < nwork; wi += gridDim.x) {
         const int b = (int)(wi / prm.nq), ql = (int)(wi % prm.nq), q = prm.q0 + ql;
         const long long lo = (long long)b * prm.ppb;
         const int n = (int)min((long long)prm.ppb, (long long)N - lo);
+        if (prm.phase_cycles && tid == 0) t_last = clock64();
 
         for (int i = tid; i < I; i += blockDim.x) s_qp[i] = prm.qproj[(size_t)i * prm.nq_total + q];
         for (int c = tid; c < dim; c += blockDim.x) qvec[c] = prm.query[(size_t)q * dim + c];
+        if (tid == 0) { s_maxpri = 0u; s_count[0] = 0; s_count[1] = 0; }
         __syncthreads();
 
         // ---- 1. split positions: warp-wide 32-ary lower bound per simple index
@@ -217,93 +312,153 @@ traverse_kernel(const TraverseParams prm) {
                 s_nl[i] = nl;
                 s_cnt[i] = nl + nr;
                 s_sp[i] = (s == n - 1 && nr > 0) ? 1 : 0;
+                s_cb[i].x = nl * T - s - 1;
+                // no window priority exceeds the distance to the farthest key
+                const float far = fmaxf(fabsf(keys[0] - qv), fabsf(keys[n - 1] - qv));
+                atomicMax(&s_maxpri, __float_as_uint(far));
             }
         }
         __syncthreads();
         if (tid < L) {
             int acc = 0;
-            for (int h = 0; h < S; ++h) { s_woff[tid * (S + 1) + h] = acc; acc += s_cnt[tid * S + h]; }
+            for (int h = 0; h < S; ++h) {
+                s_woff[tid * (S + 1) + h] = acc;
+                s_cb[tid * S + h].y = acc;
+                acc += s_cnt[tid * S + h];
+            }
             s_woff[tid * (S + 1) + S] = acc;
         }
         __syncthreads();
         int maxW = 0;
         for (int m = 0; m < L; ++m) maxW = max(maxW, s_woff[m * (S + 1) + S]);
+        const float maxpri = __uint_as_float(s_maxpri);
+        const bool buckets_ok = maxpri > 0.0f && maxpri < 3.0e38f;
+        const float scale = buckets_ok ? (float)lay.nbuckets / maxpri : 0.0f;
+        const int last_bucket = lay.nbuckets - 1;
+        DCI_PHASE_MARK(0)
 
         // ---- 2. windows, priorities, visiting order of every composite index
         for (int m = 0; m < L; ++m) {
             const int *woff = s_woff + m * (S + 1);
             const int Wm = woff[S];
-            for (int w = tid; w < Wm; w += blockDim.x) {
-                int h = 0;
-                while (w >= woff[h + 1]) ++h;
-                const int i = m * S + h, t = w - woff[h];
-                const int s = s_pos[i], nl = s_nl[i];
-                bool right; int j;
-                if (s_sp[i]) { right = (t == 0); j = right ? 0 : t - 1; }
-                else { right = (t >= nl); j = right ? t - nl : t; }
-                const int start = right ? s + 1 + j * T : s - T + 1 - j * T;
-                const int kp = right ? min(start, n - 1) : max(start, 0);
-                const float pri = fabsf(prm.skeys[(size_t)i * N + lo + kp] - s_qp[i]);
-                kA[w] = __float_as_uint(pri);
-                vA[w] = (ValT)w;
-            }
+            for (int i = tid; i <= lay.nbuckets; i += blockDim.x) cnt[i] = 0u;
             __syncthreads();
-            cta_radix_sort<ValT, ValT, true>(kA, vA, kB, vB, Wm, hist, s_scratch, rank + (size_t)m * prm.wcap);
-        }
-
-        // ---- 3. promotion iteration and lane of every point
-        for (int p = tid; p < n; p += blockDim.x) kenc[p] = 0xFFFFFFFFu;
-        for (int m = 0; m < L; ++m) {
-            const int *woff = s_woff + m * (S + 1);
-            const ValT *rk = rank + (size_t)m * prm.wcap;
-            for (int p = tid; p < n; p += blockDim.x) mr[p] = 0u;
-            __syncthreads();
-            for (int h = 0; h < S; ++h) {
-                const int i = m * S + h;
-                const int s = s_pos[i], nl = s_nl[i], sp = s_sp[i], base = woff[h];
-                const int *ids = prm.sids + (size_t)i * N + lo;
-                for (int y = tid; y < n; y += blockDim.x) {
-                    const int p = ids[y] - (int)lo;
-                    uint32_t wloc, t;
-                    if (y <= s) {
-                        const uint32_t x = (uint32_t)(s - y), j = prm.divT.div(x);
-                        t = (uint32_t)(T - 1) - (x - j * (uint32_t)T);
-                        wloc = sp ? 1u + j : j;
-                    } else {
-                        const uint32_t x = (uint32_t)(y - s - 1), j = prm.divT.div(x);
-                        t = x - j * (uint32_t)T;
-                        wloc = (uint32_t)nl + j;
+            const int gmax = prm.wcap / S;                  // no simple index has more windows than this
+            for (int h0 = 0; h0 < S; h0 += 4) {
+                for (int g = tid; g < gmax; g += blockDim.x) {
+                    float kv[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int i = m * S + h0 + u;
+                        kv[u] = 0.0f;
+                        if (h0 + u < S && g < s_cnt[i]) {
+                            const int kp = min(max(g * T - s_cb[i].x, 0), n - 1);
+                            kv[u] = __ldg(prm.skeys + (size_t)i * N + lo + kp);
+                        }
                     }
-                    const uint32_t r = (uint32_t)rk[base + wloc];
-                    atomicMax(&mr[p], (r << prm.tshift) | t);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int i = m * S + h0 + u;
+                        if (h0 + u < S && g < s_cnt[i]) {
+                            const uint32_t bits = __float_as_uint(fabsf(kv[u] - s_qp[i]));
+                            const int w = woff[h0 + u] + g;
+                            kA[w] = bits;
+                            if (buckets_ok)
+                                slot[w] = (uint8_t)min(atomicAdd(&cnt[bucket_of(bits, scale, last_bucket)], 1u), 255u);
+                        }
+                    }
                 }
             }
+            int over = buckets_ok ? 0 : 1;
             __syncthreads();
-            for (int p = tid; p < n; p += blockDim.x) {
-                const uint32_t cur = kenc[p], v = mr[p];
-                if ((v >> prm.tshift) < (cur >> prm.tshift)) kenc[p] = v;   // ties keep the lower composite
+            for (int i = tid; i < lay.nbuckets; i += blockDim.x) over |= (cnt[i] > (uint32_t)kMaxBucket);
+            over = __syncthreads_or(over);
+            DCI_PHASE_MARK(1)
+            ValT *rk = rank + (size_t)m * prm.wcap;
+            if (!over) {
+                const int *nlv = s_nl + m * S, *spv = s_sp + m * S;
+                auto tie_less = [woff, nlv, spv](uint32_t a, uint32_t b2) {
+                    int ha = 0, hb = 0;
+                    while ((int)a >= woff[ha + 1]) ++ha;
+                    while ((int)b2 >= woff[hb + 1]) ++hb;
+                    if (ha != hb) return ha < hb;
+                    return window_visit_order((int)a - woff[ha], nlv[ha], spv[ha]) <
+                           window_visit_order((int)b2 - woff[ha], nlv[ha], spv[ha]);
+                };
+                cta_bucket_place_and_rank<ValT>(kA, Wm, slot, bkey, bval, cnt, lay.nbuckets, scale, s_scratch,
+                                                rk, tie_less);
+            } else {
+                // many equal priorities: stable radix sort of the windows laid out in visiting order
+                for (int h = 0; h < S; ++h) {
+                    const int i = m * S + h, base = woff[h], nl = s_nl[i], sp = s_sp[i];
+                    for (int g = tid; g < s_cnt[i]; g += blockDim.x) {
+                        const int at = base + window_visit_order(g, nl, sp);
+                        fb_k0[at] = kA[base + g];
+                        fb_v0[at] = (ValT)(base + g);
+                    }
+                }
+                __syncthreads();
+                cta_radix_sort<ValT, ValT, true>(fb_k0, fb_v0, fb_k1, fb_v1, Wm, reinterpret_cast<ValT *>(cnt),
+                                                 s_scratch, rk);
             }
-            __syncthreads();
+            DCI_PHASE_MARK(2)
         }
 
-        // ---- 4. stop iteration from lane-0 promotions (reference :598-607)
-        if (tid == 0) { s_count[0] = 0; s_count[1] = 0; }
-        __syncthreads();
-        for (int p = tid; p < n; p += blockDim.x) {
-            const uint32_t v = kenc[p];
-            if ((v & tmask) == 0u) list[atomicAdd(&s_count[0], 1)] = v >> prm.tshift;
+        // ---- 3. promotion iteration and lane of every point; lane-0 promotions listed
+        for (int p0 = 0; p0 < n; p0 += blockDim.x) {
+            const int p = p0 + tid;
+            const bool live = p < n;
+            uint32_t best = 0xFFFFFFFFu;
+            if (live) {
+                const PosT *pp = spos + (size_t)(lo + p) * I;
+                for (int m = 0; m < L; ++m) {
+                    const ValT *rk = rank + (size_t)m * prm.wcap;
+                    uint32_t mx = 0u;
+                    for (int h0 = 0; h0 < S; h0 += 4) {
+                        uint32_t yv[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u)
+                            yv[u] = (h0 + u < S) ? (uint32_t)__ldg(pp + m * S + h0 + u) : 0u;
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            if (h0 + u < S) {
+                                const int2 cb = s_cb[m * S + h0 + u];
+                                const uint32_t x = yv[u] + (uint32_t)cb.x;       // position relative to window 0
+                                const uint32_t g = prm.divT.div(x);
+                                const uint32_t t = x - g * (uint32_t)T;
+                                const uint32_t r = (uint32_t)rk[cb.y + g];
+                                mx = max(mx, (r << prm.tshift) | t);
+                            }
+                        }
+                    }
+                    if ((mx >> prm.tshift) < (best >> prm.tshift)) best = mx;   // ties keep the lower composite
+                }
+                kenc[p] = best;
+            }
+            const bool is0 = live && (best & tmask) == 0u;
+            const int slot0 = warp_append_slot(is0, &s_count[0]);
+            if (is0) list[slot0] = (ValT)(best >> prm.tshift);
         }
         __syncthreads();
+
+        DCI_PHASE_MARK(3)
+        // ---- 4. stop iteration from lane-0 promotions (reference :598-607)
         const int cnt0 = s_count[0];
         const long long limit = (long long)n * S * T;
         long long stop = limit - 1;
         if (cnt0 >= prm.knn) {
-            const long long a = cta_kth_smallest(list, cnt0, prm.knn, (uint32_t)maxW, s_scratch);
+            const bool need_c = prm.max_cand > prm.knn && cnt0 >= prm.max_cand;
+            int bits = 1;
+            while ((1 << bits) <= maxW && bits < 31) ++bits;
+            uint32_t sel[2];
+            const ValT *lst = list;
+            cta_select2([lst](int j) { return (uint32_t)lst[j]; }, cnt0, prm.knn,
+                        need_c ? prm.max_cand : prm.knn, bits, s_sel, s_res, sel);
+            const long long a = sel[0];
             const long long bcap = max(a, prm.outer_s - 1);
             long long ccap;
             if (prm.max_cand <= prm.knn) ccap = a;
-            else if (cnt0 >= prm.max_cand)
-                ccap = max(a, (long long)cta_kth_smallest(list, cnt0, prm.max_cand, (uint32_t)maxW, s_scratch));
+            else if (need_c) ccap = max(a, (long long)sel[1]);
             else ccap = limit;
             stop = min(min(bcap, ccap), limit - 1);
         }
@@ -314,8 +469,11 @@ traverse_kernel(const TraverseParams prm) {
             lane0_stat = cta_sum(c, s_scratch);
         }
         __syncthreads();
-        for (int p = tid; p < n; p += blockDim.x) {
-            if ((long long)(kenc[p] >> prm.tshift) <= stop) list[atomicAdd(&s_count[1], 1)] = (uint32_t)p;
+        for (int p0 = 0; p0 < n; p0 += blockDim.x) {
+            const int p = p0 + tid;
+            const bool take = p < n && (long long)(kenc[p] >> prm.tshift) <= stop;
+            const int sl = warp_append_slot(take, &s_count[1]);
+            if (take) list[sl] = (ValT)p;
         }
         __syncthreads();
         const int ncand = s_count[1];
@@ -325,20 +483,15 @@ traverse_kernel(const TraverseParams prm) {
             int entries = 0;
             for (int m = 0; m < L; ++m) {
                 const int *woff = s_woff + m * (S + 1);
-                const int Wm = woff[S];
-                visits += min((long long)Wm, stop + 1);
+                visits += min((long long)woff[S], stop + 1);
                 const ValT *rk = rank + (size_t)m * prm.wcap;
-                for (int w = tid; w < Wm; w += blockDim.x) {
-                    if ((long long)rk[w] > stop) continue;
-                    int h = 0;
-                    while (w >= woff[h + 1]) ++h;
-                    const int i = m * S + h, t = w - woff[h];
-                    const int s = s_pos[i], nl = s_nl[i];
-                    bool right; int j;
-                    if (s_sp[i]) { right = (t == 0); j = right ? 0 : t - 1; }
-                    else { right = (t >= nl); j = right ? t - nl : t; }
-                    const int start = right ? s + 1 + j * T : s - T + 1 - j * T;
-                    entries += max(0, min(start + T, n) - max(start, 0));
+                for (int h = 0; h < S; ++h) {
+                    const int i = m * S + h, base = woff[h], c = s_cb[i].x;
+                    for (int g = tid; g < s_cnt[i]; g += blockDim.x) {
+                        if ((long long)rk[base + g] > stop) continue;
+                        const int start = g * T - c;
+                        entries += max(0, min(start + T, n) - max(start, 0));
+                    }
                 }
             }
             entries = cta_sum(entries, s_scratch);
@@ -350,24 +503,35 @@ traverse_kernel(const TraverseParams prm) {
             }
         }
 
+        DCI_PHASE_MARK(4)
         // ---- 5. distances of the promoted points and the partition's top-k
         CtaTopK topk;
-        topk.init(topk_buf, &s_count[0], &s_thresh, prm.topk_cap, prm.knn);
+        topk.init(topk_bufs, &s_count[0], &s_thresh, s_sel, s_res, prm.topk_cap, prm.knn);
         for (int base = 0; base < ncand; base += blockDim.x) {
             uint64_t key = kEmptySlot;
             const int j = base + tid;
-            if (j < ncand) {
+            if (SMEM && prm.vec4) {
+                const long long gid = lo + (long long)list[j < ncand ? j : 0];
+                const float d = dist_rows_tiled(prm.data, gid, qvec, dim, tiles + warp * (32 * kDistStride));
+                if (j < ncand) key = ((uint64_t)__float_as_uint(d) << 32) | (uint32_t)gid;
+            } else if (j < ncand) {
                 const long long gid = lo + (long long)list[j];
                 const float d = dist_sequential(prm.data + (size_t)gid * dim, qvec, dim, prm.vec4);
                 key = ((uint64_t)__float_as_uint(d) << 32) | (uint32_t)gid;
             }
+            DCI_PHASE_MARK(5)
             topk.offer(key);
+            DCI_PHASE_MARK(6)
         }
         topk.finish();
         uint64_t *out = prm.part_topk + ((size_t)ql * prm.num_parts + b) * prm.knn;
-        for (int j = tid; j < prm.knn; j += blockDim.x) out[j] = topk_buf[j];
+        const uint64_t *res = topk.result();
+        for (int j = tid; j < prm.knn; j += blockDim.x) out[j] = res[j];
         __syncthreads();
+        DCI_PHASE_MARK(6)
+        if (prm.phase_cycles && tid == 0) atomicAdd((unsigned long long *)&prm.phase_cycles[15], 1ull);
     }
+#undef DCI_PHASE_MARK
 }
 
 // Final top-k of one query over the per-partition lists (replaces
@@ -378,17 +542,19 @@ __global__ void merge_partitions_kernel(const uint64_t *__restrict__ part_topk, 
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     __shared__ int s_count;
     __shared__ uint64_t s_thresh;
-    uint64_t *buf = reinterpret_cast<uint64_t *>(dyn_smem);
+    __shared__ uint32_t s_sel[2][256];
+    __shared__ uint32_t s_res[4];
     const int ql = blockIdx.x;
     const uint64_t *in = part_topk + (size_t)ql * num_parts * knn;
     const long long total = (long long)num_parts * knn;
     CtaTopK topk;
-    topk.init(buf, &s_count, &s_thresh, topk_cap, knn);
+    topk.init(reinterpret_cast<uint64_t *>(dyn_smem), &s_count, &s_thresh, s_sel, s_res, topk_cap, knn);
     for (long long base = 0; base < total; base += blockDim.x) {
         const long long j = base + threadIdx.x;
         topk.offer(j < total ? in[j] : kEmptySlot);
     }
     topk.finish();
+    const uint64_t *buf = topk.result();
     for (int j = threadIdx.x; j < knn; j += blockDim.x) {
         const uint64_t key = buf[j];
         const size_t o = (size_t)(q0 + ql) * knn + j;
@@ -402,10 +568,10 @@ __global__ void merge_partitions_kernel(const uint64_t *__restrict__ part_topk, 
     }
 }
 
-// Merge of per-shard result lists for MDCI (replaces the cat/sort/gather of
-// dciknn_cuda/core.py:153-157).  One CTA per query.
 struct ShardOffsets { long long v[64]; };
 
+// Merge of per-shard result lists for MDCI (replaces the cat/sort/gather of
+// dciknn_cuda/core.py:153-157).  One CTA per query.
 __global__ void merge_shards_kernel(const int *__restrict__ ids_in, const float *__restrict__ dists_in,
                                     int num_shards, int nq, int k, int topk_cap,
                                     const ShardOffsets offsets,
@@ -413,11 +579,12 @@ __global__ void merge_shards_kernel(const int *__restrict__ ids_in, const float 
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     __shared__ int s_count;
     __shared__ uint64_t s_thresh;
-    uint64_t *buf = reinterpret_cast<uint64_t *>(dyn_smem);
+    __shared__ uint32_t s_sel[2][256];
+    __shared__ uint32_t s_res[4];
     const int q = blockIdx.x;
     const long long total = (long long)num_shards * k;
     CtaTopK topk;
-    topk.init(buf, &s_count, &s_thresh, topk_cap, k);
+    topk.init(reinterpret_cast<uint64_t *>(dyn_smem), &s_count, &s_thresh, s_sel, s_res, topk_cap, k);
     for (long long base = 0; base < total; base += blockDim.x) {
         const long long j = base + threadIdx.x;
         uint64_t key = kEmptySlot;
@@ -433,6 +600,7 @@ __global__ void merge_shards_kernel(const int *__restrict__ ids_in, const float 
         topk.offer(key);
     }
     topk.finish();
+    const uint64_t *buf = topk.result();
     for (int j = threadIdx.x; j < k; j += blockDim.x) {
         const uint64_t key = buf[j];
         const size_t o = (size_t)q * k + j;

@@ -117,7 +117,8 @@ int dci_b200_get_index(dci_b200_t *h, float *h_keys, int *h_ids);
  * fp32 path: d_out[i][p] = <proj[i], x[p]>, layout [L*S][n].  For tests. */
 int dci_b200_project(dci_b200_t *h, const float *d_x, int n, float *d_out, void *stream);
 
-/* When enabled (on != 0), every later query also records, per (query,
+/* `on` is a bit mask: bit 0 = per-work-item counters, bit 1 = per-phase cycle
+ * sums (see get_phase_cycles), 0 = off.  With bit 0 every later query also records, per (query,
  * partition) work item, what the reference's loop would have done:
  * [0] the outer iteration it stops at, [1] windows visited, [2] index entries
  * looked at, [3] points promoted, [4] promotions in lane 0, [5] 1 if every
@@ -125,6 +126,14 @@ int dci_b200_project(dci_b200_t *h, const float *d_x, int n, float *d_out, void 
  * the last query to the host as [num_queries][P][6] int64.  Synchronous. */
 int dci_b200_enable_work_stats(dci_b200_t *h, int on);
 int dci_b200_get_work_stats(dci_b200_t *h, long long *h_out, long long capacity_records);
+
+/* With bit 1 of enable_work_stats set the traversal kernel also sums, over all work
+ * items of the last query, the SM cycles one CTA spent in each of its phases:
+ * h_out (16 entries): [0] query load + split search, [1] window priorities,
+ * [2] window ordering, [3] promotion iterations, [4] stop rule + candidate
+ * list (+ the counters above), [5] distances, [6] top-k; [15] = number of work
+ * items.  Synchronous. */
+int dci_b200_get_phase_cycles(dci_b200_t *h, long long *h_out);
 
 /* Number of kernels this library launched on behalf of this handle so far. */
 long long dci_b200_launch_count(dci_b200_t *h);

@@ -48,6 +48,8 @@ EDGE_CASES = [
     ("outer_cap_hits",     5000, 16, 2, 3, 2, 10,  2, 3,     1000000,  8, None),
     ("max_cand_zero",      800,  16, 2, 3, 2, 10,  2, 5000,  0,        6, None),
     ("big_k",              900,  16, 2, 3, 3, 10, 700, 5000, 7000,     4, None),
+    ("identical_points",   700,  8,  2, 3, 2, 10, 5, 5000,  50,       4, "identical"),
+    ("two_clusters_equal", 3000, 8,  2, 4, 1, 10, 5, 5000,  50,       4, "clusters"),
 ]
 
 
@@ -58,6 +60,11 @@ def edge_case(row, seed=7):
     query = rng.standard_normal((nq, d)).astype(np.float32)
     if special == "round":
         data, query = np.round(data), np.round(query * 2) / 2
+    if special == "identical":     # every key equal: the ordering falls back to the radix sort
+        data[:] = data[0]
+    if special == "clusters":      # two groups of identical points
+        data[: N // 2] = data[0]
+        data[N // 2:] = data[1]
     if special == "far":
         query[: nq // 2] *= 30.0
     return dict(name=name, data=np.ascontiguousarray(data), query=np.ascontiguousarray(query), L=L, S=S, P=P, T=T,

@@ -26,5 +26,5 @@ def test_matches_race_fixed_reference(path):
     assert match >= 0.999, "id lists match the reference on %.2f%% of queries" % (100 * match)
     assert np.allclose(dists, z["fixed_dists"], rtol=1e-5, atol=0)
     assert (dists <= z["asis_dists"] * (1 + 1e-5)).all()      # dominance over the racy build
-    gi, _ = g.get_index()
+    _, gi = g.get_index()
     assert np.array_equal(gi.numpy(), z["ref_ids"])
