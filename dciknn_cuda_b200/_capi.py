@@ -37,6 +37,8 @@ SYMBOLS = [
     ("dci_b200_launch_count", C.c_longlong, [_vp]),
     ("dci_b200_enable_timing", C.c_int, [_vp, C.c_int]),
     ("dci_b200_get_timing", C.c_int, [_vp, _vp]),
+    ("dci_b200_query_noalloc", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                         _vp, _vp, _vp]),
     ("dci_b200_merge_shards", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, _c_llp, _vp, _vp, C.c_int, _vp]),
 ]
 

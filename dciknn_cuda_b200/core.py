@@ -168,6 +168,31 @@ class DCI(object):
                 return ids, dists
             return ids.to(torch.float32), dists     # the reference returns ids as float32 (dci_cuda.cpp:111)
 
+    def query_noalloc(self, query, ids_out, dists_out, num_outer_iterations=5000, *, max_num_candidates=None):
+        """The same query through dci_b200_query_noalloc, for callers that must not
+        trigger a device allocation (serving loops with a latency budget, processes
+        whose device memory belongs to another allocator).  The caller supplies the
+        outputs: ids_out int32 [num_queries, k] and dists_out float32 of the same
+        shape, both CUDA and contiguous; k is taken from their shape.  Working
+        memory comes from a fixed 32 MiB array inside the library, shared by all
+        calls on the device, so calls must not overlap on the GPU; oversized
+        problems raise NotImplementedError."""
+        _query = query.unsqueeze(0) if len(query.shape) < 2 else query
+        self._check_data(_query)
+        nq, k = _query.shape[0], ids_out.shape[1]
+        for t, dt in ((ids_out, torch.int32), (dists_out, torch.float32)):
+            if t.dtype != dt or not t.is_cuda or not t.is_contiguous() or tuple(t.shape) != (nq, k) \
+                    or t.device.index != self._device:
+                raise TypeError("outputs must be contiguous CUDA tensors of shape [num_queries, k]: int32 ids, float32 distances")
+        if max_num_candidates is None:
+            max_num_candidates = 10 * k
+        with torch.cuda.device(self._device):
+            _capi.check(_capi.lib().dci_b200_query_noalloc(
+                self._live(), C.c_void_p(_query.data_ptr()), nq, k, int(num_outer_iterations), int(max_num_candidates),
+                self._block_size, self._thread_size, C.c_void_p(ids_out.data_ptr()), C.c_void_p(dists_out.data_ptr()),
+                _stream_ptr(self._device)))
+        return ids_out, dists_out
+
     def query_host(self, query, num_neighbours, num_outer_iterations=5000, *, max_num_candidates=None):
         """Same query from and to HOST memory through dci_b200_query_host: `query`
         is a CPU float32 tensor; returns CPU (int32 ids, float32 distances)."""

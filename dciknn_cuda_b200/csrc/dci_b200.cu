@@ -11,6 +11,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <mutex>
 #include <new>
 
 #include "../../include/dci_b200.h"
@@ -516,3 +517,135 @@ int dci_b200_merge_shards(const int *d_ids_in, const float *d_dists_in, int num_
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Query without any allocation (see include/dci_b200.h, dci_b200_query_noalloc).
+// Its working memory is this fixed array, which every GPU that loads the
+// library holds until the process exits.  In host code the symbol below is only
+// a stand-in: the device address is obtained per device with
+// cudaGetSymbolAddress and cached.
+#define DCI_B200_NOALLOC_SCRATCH_BYTES (32u << 20)
+static __device__ __align__(256) unsigned char g_noalloc_scratch[DCI_B200_NOALLOC_SCRATCH_BYTES];
+
+namespace {
+
+std::mutex g_noalloc_mutex;
+unsigned char *g_noalloc_addr[64] = {nullptr};
+
+// Device address of g_noalloc_scratch on `device`, which must be current.
+int noalloc_scratch_address(int device, unsigned char **out) {
+    if (device < 0 || device >= 64) return fail(DCI_B200_ERR_UNSUPPORTED, "device index %d out of range for the built-in scratch", device);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (!g_noalloc_addr[device]) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || !p)
+            return fail(DCI_B200_ERR_CUDA, "cudaGetSymbolAddress(built-in scratch) failed on device %d: %s", device,
+                        cudaGetErrorString(e));
+        g_noalloc_addr[device] = (unsigned char *)p;
+    }
+    *out = g_noalloc_addr[device];
+    return 0;
+}
+
+size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+template <typename ValT, typename PosT>
+int query_noalloc_impl(dci_b200 *h, dci::TraverseParams prm, int nthreads, unsigned char *scratch, size_t avail,
+                       int num_queries, int *d_ids, float *d_dists, cudaStream_t st) {
+    auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, true);
+    cudaFuncAttributes fa;
+    DCI_CUDA(cudaFuncGetAttributes(&fa, dci::traverse_kernel<ValT, PosT, true>));
+    const size_t static_smem = fa.sharedSizeBytes;
+    if (lay.fixed_bytes + static_smem > h->smem_optin)
+        return fail(DCI_B200_ERR_UNSUPPORTED, "dim=%d needs more shared memory per CTA than the device offers", prm.dim);
+    const bool smem = lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin;
+    if (!smem) lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, false);
+    const size_t dyn = smem ? lay.fixed_bytes + lay.big_bytes : lay.fixed_bytes;
+    const size_t per_cta = align256(lay.fallback_bytes + (smem ? 0 : lay.big_bytes));
+    const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));
+    const long long max_grid = std::min<long long>((long long)num_queries * prm.num_parts, (long long)h->sm_count * per_sm);
+    const size_t slabs = per_cta * (size_t)max_grid;
+    const size_t per_query = sizeof(uint64_t) * (size_t)prm.num_parts * prm.knn;
+    if (slabs + per_query > avail)
+        return fail(DCI_B200_ERR_UNSUPPORTED,
+                    "this index and k need %zu bytes of working memory, the built-in scratch of the allocation-free query holds %u",
+                    slabs + per_query + ((size_t)DCI_B200_NOALLOC_SCRATCH_BYTES - avail), (unsigned)DCI_B200_NOALLOC_SCRATCH_BYTES);
+    const int batch = (int)std::min<size_t>((size_t)num_queries, (avail - slabs) / per_query);
+    prm.gscratch = scratch;
+    prm.gscratch_per_cta = per_cta;
+    prm.part_topk = (uint64_t *)(scratch + slabs);
+    const int merge_threads = 256;
+    const int merge_cap = next_pow2(prm.knn + merge_threads);
+    if (smem) DCI_CUDA(cudaFuncSetAttribute(dci::traverse_kernel<ValT, PosT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    else DCI_CUDA(cudaFuncSetAttribute(dci::traverse_kernel<ValT, PosT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    for (int q0 = 0; q0 < num_queries; q0 += batch) {
+        prm.q0 = q0;
+        prm.nq = std::min(batch, num_queries - q0);
+        const unsigned grid = (unsigned)std::min<long long>((long long)prm.nq * prm.num_parts, max_grid);
+        if (smem) dci::traverse_kernel<ValT, PosT, true><<<grid, nthreads, dyn, st>>>(prm);
+        else dci::traverse_kernel<ValT, PosT, false><<<grid, nthreads, dyn, st>>>(prm);
+        h->launches++;
+        DCI_CUDA(cudaGetLastError());
+        dci::merge_partitions_kernel<<<prm.nq, merge_threads, (size_t)merge_cap * 16, st>>>(
+            prm.part_topk, prm.num_parts, prm.knn, merge_cap, q0, d_ids, d_dists);
+        h->launches++;
+        DCI_CUDA(cudaGetLastError());
+    }
+    return 0;
+}
+
+}  // namespace
+
+extern "C" int dci_b200_query_noalloc(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
+                                      int num_outer_iterations, int max_num_candidates, int block_size,
+                                      int thread_size, int *d_ids, float *d_dists, void *stream) {
+    if (int rc = check_handle(h)) return rc;
+    if (h->num_points <= 0) return fail(DCI_B200_ERR_STATE, "the index is empty; add data first");
+    if (num_queries < 0) return fail(DCI_B200_ERR_ARG, "num_queries must not be negative");
+    if (num_queries == 0) return 0;
+    if (!d_query || !d_ids || !d_dists) return fail(DCI_B200_ERR_ARG, "null query or output pointer");
+    if (num_neighbours <= 0) return fail(DCI_B200_ERR_ARG, "num_neighbours must be positive, got %d", num_neighbours);
+    if (num_neighbours > h->num_points)
+        return fail(DCI_B200_ERR_ARG, "num_neighbours (%d) exceeds the number of indexed points (%d)", num_neighbours, h->num_points);
+    if (num_neighbours > dci::kMaxTopK)
+        return fail(DCI_B200_ERR_UNSUPPORTED, "num_neighbours above %d is not supported by the allocation-free query", dci::kMaxTopK);
+    if (block_size != h->P || thread_size != h->T)
+        return fail(DCI_B200_ERR_ARG, "block_size/thread_size (%d, %d) differ from the values the index was built with (%d, %d)",
+                    block_size, thread_size, h->P, h->T);
+    DeviceGuard g(h->device);
+    if (!g.ok) return fail(DCI_B200_ERR_CUDA, "cannot select device %d", h->device);
+    unsigned char *scratch = nullptr;
+    if (int rc = noalloc_scratch_address(h->device, &scratch)) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int I = h->L * h->S;
+    const size_t qproj_bytes = align256(sizeof(float) * (size_t)I * num_queries);
+    if (qproj_bytes >= (size_t)DCI_B200_NOALLOC_SCRATCH_BYTES)
+        return fail(DCI_B200_ERR_UNSUPPORTED, "%d queries need %zu bytes for their projections alone, the built-in scratch holds %u",
+                    num_queries, qproj_bytes, (unsigned)DCI_B200_NOALLOC_SCRATCH_BYTES);
+    float *qproj = (float *)scratch;
+    if (int rc = launch_project(h, d_query, num_queries, qproj, st)) return rc;
+
+    dci::TraverseParams prm;
+    memset(&prm, 0, sizeof(prm));
+    prm.skeys = (const float *)h->keys.p; prm.sids = (const int *)h->ids.p; prm.spos = h->pos.p; prm.data = h->d_data;
+    prm.qproj = qproj; prm.query = d_query;
+    prm.N = h->num_points; prm.dim = h->dim; prm.L = h->L; prm.S = h->S; prm.P = h->P; prm.T = h->T;
+    prm.ppb = h->ppb; prm.num_parts = h->num_parts; prm.nq_total = num_queries;
+    prm.knn = num_neighbours; prm.max_cand = max_num_candidates;
+    prm.outer_s = (long long)num_outer_iterations * h->S;
+    prm.wcap = h->S * ((h->ppb + h->T - 1) / h->T + 2);
+    prm.tshift = 0;
+    while ((1 << prm.tshift) < h->T) ++prm.tshift;
+    prm.divT = dci::FastDiv::make((uint32_t)h->T, (uint64_t)h->ppb + 1);
+    prm.vec4 = (h->dim % 4 == 0) && (((uintptr_t)h->d_data & 15) == 0) && (((uintptr_t)d_query & 15) == 0);
+    const int nthreads = prm.wcap >= 4096 ? 1024 : (prm.wcap >= 1024 ? 512 : 256);
+    prm.topk_cap = next_pow2(num_neighbours + nthreads);
+    unsigned char *rest = scratch + qproj_bytes;
+    const size_t avail = (size_t)DCI_B200_NOALLOC_SCRATCH_BYTES - qproj_bytes;
+    if (prm.ppb <= 65535)
+        return (prm.wcap <= 65535)
+                   ? query_noalloc_impl<uint16_t, uint16_t>(h, prm, nthreads, rest, avail, num_queries, d_ids, d_dists, st)
+                   : query_noalloc_impl<uint32_t, uint16_t>(h, prm, nthreads, rest, avail, num_queries, d_ids, d_dists, st);
+    return query_noalloc_impl<uint32_t, uint32_t>(h, prm, nthreads, rest, avail, num_queries, d_ids, d_dists, st);
+}

@@ -159,6 +159,39 @@ int dci_b200_merge_shards(const int *d_ids_in, const float *d_dists_in, int num_
                           int num_queries, int k, const long long *id_offsets,
                           long long *d_ids_out, float *d_dists_out, int device, void *stream);
 
+/* Query for callers that must not allocate.  (No counterpart in the reference,
+ * which allocates and frees managed and device memory inside every query,
+ * src/dci_cuda_kernel.cu:792-831, 868-874.)
+ *
+ * dci_b200_query grows per-handle work buffers with cudaMalloc when a call
+ * needs more room than the previous ones did.  Some callers cannot tolerate
+ * that: a serving loop with a latency budget (cudaMalloc and cudaFree
+ * synchronise the whole device), a process whose device memory is owned
+ * entirely by another allocator or is already full, a plugin host that forbids
+ * driver allocations after start-up.  This entry point answers the same query,
+ * with the same results, and calls no cudaMalloc, cudaFree or other allocating
+ * routine: its working memory (projected queries, per-partition result lists,
+ * per-CTA slabs) is carved from one fixed array of
+ * DCI_B200_NOALLOC_SCRATCH_BYTES bytes that is part of the library image, so
+ * every GPU that loads the library holds that much memory until the process
+ * exits.  The caller passes the inputs and the outputs exactly as for
+ * dci_b200_query (blind querying is not offered).
+ *
+ * Limits: the query is rejected with DCI_B200_ERR_UNSUPPORTED, and a message
+ * that states the need, when the index geometry and k do not fit the array
+ * even for a single query (the per-CTA slabs grow with the partition size);
+ * larger query batches are processed in as many passes as fit.
+ * The first call on a device looks the array's device address up
+ * (cudaGetSymbolAddress); make that first call before any stream capture.
+ * All calls on a device share the array and it keeps the previous call's
+ * contents; nothing in it needs to start at zero.  Two calls that overlap on
+ * the GPU (different streams or threads, same device) race on it: serialise
+ * them.  Work statistics and timing are not recorded on this path. */
+#define DCI_B200_NOALLOC_SCRATCH_BYTES (32u << 20)
+int dci_b200_query_noalloc(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
+                           int num_outer_iterations, int max_num_candidates, int block_size,
+                           int thread_size, int *d_ids, float *d_dists, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
