@@ -397,10 +397,13 @@ class MDCI(object):
             eng = self.dcis[0]
             q = _query.to(eng.device).contiguous() if isinstance(eng, DCI) else _query
             a, d = eng.query(q, k, num_outer_iterations, max_num_candidates=max_num_candidates, return_int_ids=True)
-            ids = torch.empty((self.num_devices,) + tuple(a.shape), dtype=a.dtype, device=a.device)
-            dists = torch.empty((self.num_devices,) + tuple(d.shape), dtype=d.dtype, device=d.device)
-            self._dist.all_gather_into_tensor(ids, a.contiguous(), group=self._pg)
+            nq = a.shape[0]
+            ids = torch.empty((self.num_devices * nq, k), dtype=a.dtype, device=a.device)
+            dists = torch.empty((self.num_devices * nq, k), dtype=d.dtype, device=d.device)
+            self._dist.all_gather_into_tensor(ids, a.contiguous(), group=self._pg)      # rank-major concatenation
             self._dist.all_gather_into_tensor(dists, d.contiguous(), group=self._pg)
+            ids = ids.view(self.num_devices, nq, k)
+            dists = dists.view(self.num_devices, nq, k)
         offsets = [self.data_per_device * i for i in range(self.num_devices)]
         out_ids, out_dists = self._merge(ids, dists, offsets, k)
         if return_int_ids:
