@@ -1,0 +1,68 @@
+"""Parity against the reference's own CUDA build run on the same GPU with the
+same projection directions (skipped when oracle/_ref was not built).
+
+Criteria of the headline comparison: neighbour id lists identical to the
+race-fixed reference for >= 99.9 % of queries, distances within 1e-5 relative,
+recall@k against exact brute force no worse than the unmodified reference's,
+and every distance no larger than the unmodified reference's (which returns the
+top-k of a subset of the same candidates)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests import cases
+
+pytestmark = pytest.mark.gpu
+
+
+def _recall(ids, truth):
+    return float(np.mean([len(set(a) & set(b)) / len(b) for a, b in zip(ids, truth)]))
+
+
+def _compare(c, nq_ref):
+    from oracle import reference
+    if not (reference.available() and reference.available(race_fixed=True)):
+        pytest.skip("reference build (oracle/_ref) not present")
+    from dciknn_cuda_b200 import DCI
+    dim = c["data"].shape[1]
+    data = torch.from_numpy(c["data"]).cuda()
+    query = torch.from_numpy(c["query"][:nq_ref]).cuda()
+    out = {}
+    proj = None
+    for tag, fixed in (("asis", False), ("fixed", True)):
+        ref = reference.ReferenceDCI(dim, c["L"], c["S"], c["P"], c["T"], 0, race_fixed=fixed)
+        if proj is None:
+            proj = ref.get_proj()
+        else:
+            ref.set_proj(proj)
+        ref.add(data)
+        ids, dists = ref.query(query, c["k"], c["outer"])
+        out[tag] = (ids.cpu().numpy(), dists.cpu().numpy())
+        ref.free()
+    g = DCI(dim, c["L"], c["S"], c["P"], c["T"], 0, proj=torch.from_numpy(proj))
+    g.add(data)
+    ids, dists = g.query(query, c["k"], c["outer"], return_int_ids=True)
+    ids, dists = ids.cpu().numpy(), dists.cpu().numpy()
+    fi, fd = out["fixed"]
+    ai, ad = out["asis"]
+    match = float((ids == fi).all(1).mean())
+    truth, _ = oracle.bruteforce(c["data"], c["query"][:nq_ref], c["k"])
+    r_ours, r_fixed, r_asis = _recall(ids, truth), _recall(fi, truth), _recall(ai, truth)
+    print("id-list match vs race-fixed reference: %.4f; recall ours %.4f, race-fixed %.4f, as-is %.4f"
+          % (match, r_ours, r_fixed, r_asis))
+    assert match >= 0.999
+    same = ids == fi
+    assert np.allclose(dists[same], fd[same], rtol=1e-5, atol=0)
+    assert r_ours >= r_asis and r_ours >= r_fixed - 1e-3
+    assert (dists <= ad * (1 + 1e-5)).all()
+
+
+def test_example_configuration_against_reference_build():
+    c = cases.example_config()           # configs[0]: 2000 x 100, 500 queries
+    _compare(c, 500)
+
+
+def test_c2_shaped_against_reference_build():
+    c = cases.c2_shaped(n=40000, nq=192, P=4)   # partitions of 10 000 points as in configs[1]
+    _compare(c, 192)
