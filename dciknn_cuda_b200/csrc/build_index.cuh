@@ -3,11 +3,10 @@
 // of the reference (src/dci_cuda_kernel.cu:113-146, 190-247).  The result is
 // kept as flat arrays keys[L*S][N] / ids[L*S][N] (SoA) instead of the
 // reference's array of {key, id} structs (include/dci.h:27-30), plus the
-// inverse permutation pos[N][L*S] (point-major, so that one point's positions
-// are contiguous): pos[p][i] = position of point p inside its partition's
-// sorted segment of simple index i (16-bit when partitions hold fewer than
-// 65 536 points), which lets a query look a point's window up directly instead
-// of scattering over index entries.
+// inverse permutation pos[L*S][N]: pos[i][p] = position of point p inside its
+// partition's sorted segment of simple index i (16-bit when partitions hold
+// fewer than 65 536 points), which lets a query look a point's window up
+// directly instead of scattering over index entries.
 // Equal keys are ordered by id (the input order), which the reference leaves
 // unspecified.
 #pragma once
@@ -61,7 +60,7 @@ build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_in
         for (int x = threadIdx.x; x < n; x += blockDim.x) {
             skeys[row + x] = ordered_to_float(kA[x]);
             sids[row + x] = (int)(lo + vA[x]);
-            spos[(size_t)(lo + vA[x]) * num_indices + i] = (ValT)x;
+            spos[row + vA[x]] = (ValT)x;
         }
         __syncthreads();
     }

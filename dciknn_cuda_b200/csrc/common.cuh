@@ -26,31 +26,27 @@ __device__ __forceinline__ float ordered_to_float(uint32_t u) {
     return __uint_as_float((u & 0x80000000u) ? (u & 0x7FFFFFFFu) : ~u);
 }
 
-// Exact unsigned division by a runtime-constant divisor d >= 1 for x < limit,
-// limit = 2^32 / d (see FastDiv::ok).  Falls back to '/' otherwise.
+// Exact unsigned division by a runtime-constant divisor d >= 1, branch-free:
+// x / d = umulhi(x, magic) + x * unit with magic = floor(2^32 / d) + 1, unit = 0
+// for d >= 2 (exact while x * d < 2^32) and magic = 0, unit = 1 for d = 1.
 struct FastDiv {
-    uint32_t d, magic;
-    int fast;
-    __host__ __device__ static FastDiv make(uint32_t d, uint64_t max_x) {
+    uint32_t magic, unit;
+    __host__ __device__ static FastDiv make(uint32_t d) {
         FastDiv f;
-        f.d = d;
-        f.magic = 0;
-        f.fast = 0;
-        if (d > 1 && max_x < (0x100000000ull / d)) {
-            f.magic = (uint32_t)(0x100000000ull / d) + 1u;
-            f.fast = 1;
-        }
+        f.magic = d > 1 ? (uint32_t)(0x100000000ull / d) + 1u : 0u;
+        f.unit = d > 1 ? 0u : 1u;
         return f;
     }
-    __device__ __forceinline__ uint32_t div(uint32_t x) const {
-        if (d == 1) return x;
-        return fast ? __umulhi(x, magic) : x / d;
+    __host__ __device__ static bool exact_for(uint32_t d, uint64_t max_x) {
+        return d == 1 || max_x * d < 0x100000000ull;
     }
+    __device__ __forceinline__ uint32_t div(uint32_t x) const { return __umulhi(x, magic) + x * unit; }
 };
 
 // Exclusive scan, in place, of a[0..n) by the whole CTA; also returns the total
 // to every thread.  scratch: 33 shared words.  Ends with a barrier.
-__device__ __forceinline__ uint32_t cta_exclusive_scan_u32(uint32_t *a, int n, uint32_t *scratch) {
+template <typename T>
+__device__ __forceinline__ uint32_t cta_exclusive_scan(T *a, int n, uint32_t *scratch) {
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, nw = blockDim.x >> 5;
     const int per = (n + blockDim.x - 1) / blockDim.x;
     const int lo = min(tid * per, n), hi = min(lo + per, n);
@@ -77,10 +73,23 @@ __device__ __forceinline__ uint32_t cta_exclusive_scan_u32(uint32_t *a, int n, u
     }
     __syncthreads();
     uint32_t base = scratch[w] + inc - sum;
-    for (int j = lo; j < hi; ++j) { const uint32_t v = a[j]; a[j] = base; base += v; }
+    for (int j = lo; j < hi; ++j) { const uint32_t v = a[j]; a[j] = (T)base; base += v; }
     const uint32_t total = scratch[32];
     __syncthreads();
     return total;
+}
+__device__ __forceinline__ uint32_t cta_exclusive_scan_u32(uint32_t *a, int n, uint32_t *scratch) {
+    return cta_exclusive_scan<uint32_t>(a, n, scratch);
+}
+
+// Bucket counters are 32-bit, or 16-bit packed two to a word (counts must then
+// stay below 65 536, which holds whenever the number of keys does).  arrive()
+// adds one to bucket b and returns the previous count.
+__device__ __forceinline__ uint32_t bucket_arrive(uint32_t *cnt, int b) { return atomicAdd(&cnt[b], 1u); }
+__device__ __forceinline__ uint32_t bucket_arrive(uint16_t *cnt, int b) {
+    uint32_t *word = reinterpret_cast<uint32_t *>(cnt) + (b >> 1);
+    const int sh = (b & 1) << 4;
+    return (atomicAdd(word, 1u << sh) >> sh) & 0xFFFFu;
 }
 
 // Stable LSD radix sort of W (u32 key, ValT payload) pairs by one CTA, 8 bits
@@ -175,13 +184,13 @@ __device__ __forceinline__ int bucket_of(uint32_t key_bits, float scale, int las
 // rank in ascending (key, tie order): rank = start of its bucket + number of
 // smaller keys inside the bucket.  tie_less(a, b) orders two key indices whose
 // keys are equal.  rank_out[w] receives the rank.  Ends with a barrier.
-template <typename ValT, typename TieLess>
+template <typename ValT, typename CntT, typename TieLess>
 __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, int W, const uint8_t *slot,
-                                                          uint32_t *bkey, ValT *bval, uint32_t *cnt,
+                                                          uint32_t *bkey, ValT *bval, CntT *cnt,
                                                           int nbuckets, float scale, uint32_t *scratch,
                                                           ValT *rank_out, TieLess tie_less) {
     const int tid = threadIdx.x, last = nbuckets - 1;
-    cta_exclusive_scan_u32(cnt, nbuckets + 1, scratch);      // cnt[b] = start of bucket b, cnt[nbuckets] = W
+    cta_exclusive_scan<CntT>(cnt, nbuckets + 1, scratch);    // cnt[b] = start of bucket b, cnt[nbuckets] = W
     for (int w = tid; w < W; w += blockDim.x) {
         const uint32_t k = key[w];
         const uint32_t pos = cnt[bucket_of(k, scale, last)] + (uint32_t)slot[w];

@@ -74,7 +74,7 @@ struct dci_b200 {
     const float *d_data = nullptr;       // borrowed
     float *d_proj = nullptr;             // [L*S][dim]
     Buf keys, ids, pos;                  // [L*S][N] sorted index and inverse positions
-    Buf tmp_keys, qproj, part_topk, scratch, stats, phases, hq, hids, hdists;
+    Buf tmp_keys, qproj, part_topk, scratch, merge_scratch, stats, phases, hq, hids, hdists;
     int stats_on = 0, stats_nq = 0, phases_valid = 0;
     int timing_on = 0;
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -138,20 +138,38 @@ int launch_build(dci_b200 *h, const float *d_unsorted, cudaStream_t st) {
     return 0;
 }
 
+// Number of value buckets for the window ordering: as many as twice the windows
+// of a composite index (so that most buckets hold at most one window) while the
+// whole work item still fits shared memory, else fewer.
+template <typename ValT>
+int pick_buckets(dci_b200 *h, const dci::TraverseParams &prm, int nthreads, size_t static_smem) {
+    const int choices[3] = {2 * prm.wcap, prm.wcap, prm.wcap / 2};
+    for (int c = 0; c < 3; ++c) {
+        const int nb = std::min(std::max(choices[c], 64), 1 << 20);
+        const auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_global ? 0 : prm.topk_cap, prm.L,
+                                                         prm.wcap, prm.ppb, nb, true);
+        if (lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin) return nb;
+    }
+    return std::min(std::max(prm.wcap / 2, 64), 16384);
+}
+
 template <typename ValT, typename PosT>
 int launch_traverse(dci_b200 *h, dci::TraverseParams prm, int nthreads, cudaStream_t st) {
-    auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, true);
     const long long nwork = (long long)prm.nq * prm.num_parts;
     cudaFuncAttributes fa;
     DCI_CUDA(cudaFuncGetAttributes(&fa, dci::traverse_kernel<ValT, PosT, true>));
     const size_t static_smem = fa.sharedSizeBytes;
+    prm.nbuckets = pick_buckets<ValT>(h, prm, nthreads, static_smem);
+    const int cap_smem = prm.topk_global ? 0 : prm.topk_cap;
+    auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, cap_smem, prm.L, prm.wcap, prm.ppb, prm.nbuckets, true);
     if (lay.fixed_bytes + static_smem > h->smem_optin)
         return fail(DCI_B200_ERR_UNSUPPORTED, "dim=%d with k=%d needs %zu bytes of shared memory per CTA, more than the device offers",
                     prm.dim, prm.knn, lay.fixed_bytes + static_smem);
     const bool smem = lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin;
-    if (!smem) lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, false);
+    if (!smem) lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, cap_smem, prm.L, prm.wcap, prm.ppb, prm.nbuckets, false);
     const size_t dyn = smem ? lay.fixed_bytes + lay.big_bytes : lay.fixed_bytes;
-    const size_t per_cta = lay.fallback_bytes + (smem ? 0 : lay.big_bytes);
+    prm.topk_global_off = lay.fallback_bytes + (smem ? 0 : lay.big_bytes);
+    const size_t per_cta = prm.topk_global_off + (prm.topk_global ? (size_t)prm.topk_cap * 16 : 0);
     const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));
     const unsigned grid = (unsigned)std::min<long long>(nwork, (long long)h->sm_count * per_sm);
     DCI_CUDA(h->scratch.ensure(per_cta * grid));
@@ -223,7 +241,7 @@ int dci_b200_destroy(dci_b200_t *h) {
     if (!h) return 0;
     DeviceGuard g(h->device);
     cudaDeviceSynchronize();
-    Buf *bufs[] = {&h->keys, &h->ids, &h->pos, &h->tmp_keys, &h->qproj, &h->part_topk, &h->scratch, &h->stats, &h->phases,
+    Buf *bufs[] = {&h->keys, &h->ids, &h->pos, &h->tmp_keys, &h->qproj, &h->part_topk, &h->scratch, &h->merge_scratch, &h->stats, &h->phases,
                    &h->hq, &h->hids, &h->hdists};
     for (Buf *b : bufs) b->release();
     if (h->d_proj) cudaFree(h->d_proj);
@@ -269,8 +287,10 @@ int dci_b200_add(dci_b200_t *h, const float *d_data, int num_points, int block_s
         int tshift = 0;
         while ((1 << tshift) < thread_size) ++tshift;
         const unsigned long long wcap = (unsigned long long)h->S * ((ppb + thread_size - 1) / thread_size + 2);
-        if ((wcap << tshift) >= 0xFFFFFFFFull)
-            return fail(DCI_B200_ERR_UNSUPPORTED, "partition of %d points with %d simple indices is too large", ppb, h->S);
+        if ((wcap << tshift) >= 0xFFFFFFFFull ||
+            !dci::FastDiv::exact_for((uint32_t)thread_size, (uint64_t)ppb + 2ull * thread_size))
+            return fail(DCI_B200_ERR_UNSUPPORTED, "partition of %d points with %d simple indices and thread_size %d is too large",
+                        ppb, h->S, thread_size);
     }
     const size_t n_entries = (size_t)I * num_points;
     DCI_CUDA(h->keys.ensure(n_entries * sizeof(float)));
@@ -298,8 +318,6 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
     if (num_neighbours <= 0) return fail(DCI_B200_ERR_ARG, "num_neighbours must be positive, got %d", num_neighbours);
     if (num_neighbours > h->num_points)
         return fail(DCI_B200_ERR_ARG, "num_neighbours (%d) exceeds the number of indexed points (%d)", num_neighbours, h->num_points);
-    if (num_neighbours > dci::kMaxTopK)
-        return fail(DCI_B200_ERR_UNSUPPORTED, "num_neighbours above %d is not supported yet", dci::kMaxTopK);
     if (block_size != h->P || thread_size != h->T)
         return fail(DCI_B200_ERR_ARG, "block_size/thread_size (%d, %d) differ from the values the index was built with (%d, %d)",
                     block_size, thread_size, h->P, h->T);
@@ -328,12 +346,16 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
     prm.wcap = h->S * ((h->ppb + h->T - 1) / h->T + 2);
     prm.tshift = 0;
     while ((1 << prm.tshift) < h->T) ++prm.tshift;
-    prm.divT = dci::FastDiv::make((uint32_t)h->T, (uint64_t)h->ppb + 1);
+    prm.divT = dci::FastDiv::make((uint32_t)h->T);
     prm.vec4 = (h->dim % 4 == 0) && (((uintptr_t)h->d_data & 15) == 0) && (((uintptr_t)d_query & 15) == 0);
+    prm.vec8 = (h->dim % 8 == 0) && (((uintptr_t)h->d_data & 31) == 0);
     const int nthreads = prm.wcap >= 4096 ? 1024 : (prm.wcap >= 1024 ? 512 : 256);
-    prm.topk_cap = next_pow2(num_neighbours + nthreads);
+    prm.kpart = std::min(num_neighbours, h->ppb);
+    prm.topk_cap = next_pow2(prm.kpart + nthreads);
+    prm.topk_global = prm.topk_cap > 2048 ? 1 : 0;      // larger selection buffers do not fit shared memory
     const int merge_threads = 256;
     const int merge_cap = next_pow2(num_neighbours + merge_threads);
+    const bool merge_global = merge_cap > 2048;
 
     if (h->stats_on & 2) {
         DCI_CUDA(h->phases.ensure(sizeof(long long) * 16));
@@ -348,10 +370,12 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
         prm.work_stats = (long long *)h->stats.p;
         h->stats_nq = num_queries;
     }
-    const size_t per_query = sizeof(uint64_t) * (size_t)h->num_parts * num_neighbours;
+    const size_t per_query = sizeof(uint64_t) * (size_t)h->num_parts * prm.kpart;
     const int batch = (int)std::max<size_t>(1, std::min<size_t>((size_t)num_queries, ((size_t)1 << 30) / per_query));
     DCI_CUDA(h->part_topk.ensure(per_query * batch));
     prm.part_topk = (uint64_t *)h->part_topk.p;
+    const int merge_grid_cap = merge_global ? 2 * h->sm_count : (1 << 30);
+    if (merge_global) DCI_CUDA(h->merge_scratch.ensure((size_t)merge_grid_cap * 2 * merge_cap * sizeof(uint64_t)));
     for (int q0 = 0; q0 < num_queries; q0 += batch) {
         prm.q0 = q0;
         prm.nq = std::min(batch, num_queries - q0);
@@ -364,8 +388,10 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
             rc = launch_traverse<uint32_t, uint32_t>(h, prm, nthreads, st);
         if (rc) return rc;
         if (timing) DCI_CUDA(cudaEventRecord(h->ev[3], st));
-        dci::merge_partitions_kernel<<<prm.nq, merge_threads, (size_t)merge_cap * 16, st>>>(
-            prm.part_topk, h->num_parts, num_neighbours, merge_cap, q0, d_ids, d_dists);
+        dci::merge_partitions_kernel<<<std::min(prm.nq, merge_grid_cap), merge_threads,
+                                       merge_global ? 0 : (size_t)merge_cap * 16, st>>>(
+            prm.part_topk, h->num_parts, prm.kpart, num_neighbours, merge_cap, q0, prm.nq,
+            merge_global ? (uint64_t *)h->merge_scratch.p : nullptr, d_ids, d_dists);
         h->launches++;
         DCI_CUDA(cudaGetLastError());
         if (timing) {   // timing mode synchronises after every batch; it is off by default
@@ -553,20 +579,21 @@ size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
 template <typename ValT, typename PosT>
 int query_noalloc_impl(dci_b200 *h, dci::TraverseParams prm, int nthreads, unsigned char *scratch, size_t avail,
                        int num_queries, int *d_ids, float *d_dists, cudaStream_t st) {
-    auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, true);
     cudaFuncAttributes fa;
     DCI_CUDA(cudaFuncGetAttributes(&fa, dci::traverse_kernel<ValT, PosT, true>));
     const size_t static_smem = fa.sharedSizeBytes;
+    prm.nbuckets = pick_buckets<ValT>(h, prm, nthreads, static_smem);
+    auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, prm.nbuckets, true);
     if (lay.fixed_bytes + static_smem > h->smem_optin)
         return fail(DCI_B200_ERR_UNSUPPORTED, "dim=%d needs more shared memory per CTA than the device offers", prm.dim);
     const bool smem = lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin;
-    if (!smem) lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, false);
+    if (!smem) lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, prm.nbuckets, false);
     const size_t dyn = smem ? lay.fixed_bytes + lay.big_bytes : lay.fixed_bytes;
     const size_t per_cta = align256(lay.fallback_bytes + (smem ? 0 : lay.big_bytes));
     const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));
     const long long max_grid = std::min<long long>((long long)num_queries * prm.num_parts, (long long)h->sm_count * per_sm);
     const size_t slabs = per_cta * (size_t)max_grid;
-    const size_t per_query = sizeof(uint64_t) * (size_t)prm.num_parts * prm.knn;
+    const size_t per_query = sizeof(uint64_t) * (size_t)prm.num_parts * prm.kpart;
     if (slabs + per_query > avail)
         return fail(DCI_B200_ERR_UNSUPPORTED,
                     "this index and k need %zu bytes of working memory, the built-in scratch of the allocation-free query holds %u",
@@ -588,7 +615,7 @@ int query_noalloc_impl(dci_b200 *h, dci::TraverseParams prm, int nthreads, unsig
         h->launches++;
         DCI_CUDA(cudaGetLastError());
         dci::merge_partitions_kernel<<<prm.nq, merge_threads, (size_t)merge_cap * 16, st>>>(
-            prm.part_topk, prm.num_parts, prm.knn, merge_cap, q0, d_ids, d_dists);
+            prm.part_topk, prm.num_parts, prm.kpart, prm.knn, merge_cap, q0, prm.nq, nullptr, d_ids, d_dists);
         h->launches++;
         DCI_CUDA(cudaGetLastError());
     }
@@ -637,10 +664,11 @@ extern "C" int dci_b200_query_noalloc(dci_b200_t *h, const float *d_query, int n
     prm.wcap = h->S * ((h->ppb + h->T - 1) / h->T + 2);
     prm.tshift = 0;
     while ((1 << prm.tshift) < h->T) ++prm.tshift;
-    prm.divT = dci::FastDiv::make((uint32_t)h->T, (uint64_t)h->ppb + 1);
+    prm.divT = dci::FastDiv::make((uint32_t)h->T);
     prm.vec4 = (h->dim % 4 == 0) && (((uintptr_t)h->d_data & 15) == 0) && (((uintptr_t)d_query & 15) == 0);
     const int nthreads = prm.wcap >= 4096 ? 1024 : (prm.wcap >= 1024 ? 512 : 256);
-    prm.topk_cap = next_pow2(num_neighbours + nthreads);
+    prm.kpart = std::min(num_neighbours, h->ppb);
+    prm.topk_cap = next_pow2(prm.kpart + nthreads);
     unsigned char *rest = scratch + qproj_bytes;
     const size_t avail = (size_t)DCI_B200_NOALLOC_SCRATCH_BYTES - qproj_bytes;
     if (prm.ppb <= 65535)

@@ -41,7 +41,7 @@ namespace dci {
 struct TraverseParams {
     const float *skeys;        // [I][N] sorted keys
     const int *sids;           // [I][N] point ids
-    const void *spos;          // [N][I] position of each point in its sorted segments (u16 or u32)
+    const void *spos;          // [I][N] position of each point in its sorted segment (u16 or u32)
     const float *data;         // [N][dim]
     const float *qproj;        // [I][nq_total]
     const float *query;        // [nq_total][dim]
@@ -55,12 +55,18 @@ struct TraverseParams {
     int nq, nq_total, q0;      // this launch covers queries [q0, q0 + nq)
     int knn, max_cand;
     int wcap;                  // capacity of one composite's window list
-    int topk_cap;              // power of two >= knn + blockDim.x
+    int nbuckets;              // value buckets of the window ordering
+    int kpart;                 // length of a partition's result list: min(knn, ppb)
+    int topk_cap;              // power of two >= kpart + blockDim.x
+    int topk_global;           // 1: the top-k buffers live in the CTA's global slab (large k)
+    size_t topk_global_off;    // their offset inside the slab
     int tshift;                // bits that hold the lane in an encoded promotion
     int vec4;                  // rows of data/query can be read as float4
+    int vec8;                  // rows of data start on 32-byte boundaries: one full sector per load
     FastDiv divT;
 };
 
+constexpr int kPromoPoints = 5;                // points a thread carries through the promotion phase
 constexpr int kDistChunk = 16;                 // floats of a row staged per step of the distance phase
 constexpr int kDistStride = kDistChunk + 4;    // padded row stride of the staging tile (floats)
 
@@ -79,14 +85,11 @@ struct TraverseLayout {
     size_t fallback_bytes;
     __host__ __device__ static size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
     __host__ __device__ static TraverseLayout make(int nthreads, int dim, int topk_cap, int L,
-                                                   int wcap, int ppb, bool smem) {
+                                                   int wcap, int ppb, int nbuckets, bool smem) {
         TraverseLayout l;
         const size_t radix_hist = (size_t)256 * (nthreads / 32) * sizeof(ValT);
-        int nb = wcap / 2;
-        if (nb < 64) nb = 64;
-        if (nb > 8190) nb = 8190;
-        l.nbuckets = nb;
-        const size_t bucket_cnt = (size_t)4 * (nb + 1);
+        l.nbuckets = nbuckets;
+        const size_t bucket_cnt = sizeof(ValT) * (size_t)(nbuckets + 2);
         l.cnt_bytes = align16(radix_hist > bucket_cnt ? radix_hist : bucket_cnt);
         l.qvec_bytes = align16((size_t)dim * 4);
         l.fixed_bytes = l.cnt_bytes + l.qvec_bytes;
@@ -152,6 +155,33 @@ __device__ __forceinline__ float dist_sequential(const float *__restrict__ row, 
             const float d = __fsub_rn(__ldg(row + c), qv[c]);
             sq = __fmaf_rn(d, d, sq);
         }
+    }
+    return __fsqrt_rn(sq);
+}
+
+// Same distance with one 256-bit load per step: each lane fetches one whole
+// 32-byte sector of its own row (sm_100 has 256-bit global loads), so no bytes
+// are fetched that the lane does not use and no shared staging is needed.
+// Requires dim % 8 == 0 and rows on 32-byte boundaries.
+__device__ __forceinline__ float dist_sequential_v8(const float *__restrict__ row, const float *qv, int dim) {
+    float sq = 0.0f;
+    const int n8 = dim >> 3;
+#pragma unroll 2
+    for (int c = 0; c < n8; ++c) {
+        float a0, a1, a2, a3, a4, a5, a6, a7;
+        asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                     : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3), "=f"(a4), "=f"(a5), "=f"(a6), "=f"(a7)
+                     : "l"(row + c * 8));
+        const float4 b0 = *reinterpret_cast<const float4 *>(qv + c * 8);
+        const float4 b1 = *reinterpret_cast<const float4 *>(qv + c * 8 + 4);
+        float d = __fsub_rn(a0, b0.x); sq = __fmaf_rn(d, d, sq);
+        d = __fsub_rn(a1, b0.y); sq = __fmaf_rn(d, d, sq);
+        d = __fsub_rn(a2, b0.z); sq = __fmaf_rn(d, d, sq);
+        d = __fsub_rn(a3, b0.w); sq = __fmaf_rn(d, d, sq);
+        d = __fsub_rn(a4, b1.x); sq = __fmaf_rn(d, d, sq);
+        d = __fsub_rn(a5, b1.y); sq = __fmaf_rn(d, d, sq);
+        d = __fsub_rn(a6, b1.z); sq = __fmaf_rn(d, d, sq);
+        d = __fsub_rn(a7, b1.w); sq = __fmaf_rn(d, d, sq);
     }
     return __fsqrt_rn(sq);
 }
@@ -240,8 +270,9 @@ traverse_kernel(const TraverseParams prm) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     const int L = prm.L, S = prm.S, T = prm.T, I = L * S, N = prm.N, dim = prm.dim;
     const TraverseLayout<ValT> lay =
-        TraverseLayout<ValT>::make(blockDim.x, dim, prm.topk_cap, L, prm.wcap, prm.ppb, SMEM);
-    uint32_t *cnt = reinterpret_cast<uint32_t *>(dyn_smem);            // bucket counters / radix histogram
+        TraverseLayout<ValT>::make(blockDim.x, dim, prm.topk_global ? 0 : prm.topk_cap, L, prm.wcap, prm.ppb,
+                                   prm.nbuckets, SMEM);
+    ValT *cnt = reinterpret_cast<ValT *>(dyn_smem);                    // bucket counters / radix histogram
     float *qvec = reinterpret_cast<float *>(dyn_smem + lay.cnt_bytes);
     unsigned char *slab = prm.gscratch + (size_t)blockIdx.x * prm.gscratch_per_cta;
     unsigned char *big = SMEM ? dyn_smem + lay.fixed_bytes : slab + lay.fallback_bytes;
@@ -261,7 +292,8 @@ traverse_kernel(const TraverseParams prm) {
     uint32_t *kenc = reinterpret_cast<uint32_t *>(uni);                       // best promotion per point
     ValT *list = reinterpret_cast<ValT *>(uni + lay.list_off);                // lane-0 ranks, then candidates
     // distance view
-    uint64_t *topk_bufs = reinterpret_cast<uint64_t *>(uni);                  // over kenc, phase 5 only
+    uint64_t *topk_bufs = prm.topk_global ? reinterpret_cast<uint64_t *>(slab + prm.topk_global_off)
+                                          : reinterpret_cast<uint64_t *>(uni);   // over kenc, phase 5 only
     float *tiles = reinterpret_cast<float *>(uni + lay.topk_bytes);           // staging, shared variant only
     const PosT *spos = reinterpret_cast<const PosT *>(prm.spos);
 
@@ -341,7 +373,7 @@ traverse_kernel(const TraverseParams prm) {
         for (int m = 0; m < L; ++m) {
             const int *woff = s_woff + m * (S + 1);
             const int Wm = woff[S];
-            for (int i = tid; i <= lay.nbuckets; i += blockDim.x) cnt[i] = 0u;
+            for (int i = tid; i < lay.nbuckets + 2; i += blockDim.x) cnt[i] = 0;
             __syncthreads();
             const int gmax = prm.wcap / S;                  // no simple index has more windows than this
             for (int h0 = 0; h0 < S; h0 += 4) {
@@ -364,14 +396,14 @@ traverse_kernel(const TraverseParams prm) {
                             const int w = woff[h0 + u] + g;
                             kA[w] = bits;
                             if (buckets_ok)
-                                slot[w] = (uint8_t)min(atomicAdd(&cnt[bucket_of(bits, scale, last_bucket)], 1u), 255u);
+                                slot[w] = (uint8_t)min(bucket_arrive(cnt, bucket_of(bits, scale, last_bucket)), 255u);
                         }
                     }
                 }
             }
             int over = buckets_ok ? 0 : 1;
             __syncthreads();
-            for (int i = tid; i < lay.nbuckets; i += blockDim.x) over |= (cnt[i] > (uint32_t)kMaxBucket);
+            for (int i = tid; i < lay.nbuckets; i += blockDim.x) over |= ((uint32_t)cnt[i] > (uint32_t)kMaxBucket);
             over = __syncthreads_or(over);
             DCI_PHASE_MARK(1)
             ValT *rk = rank + (size_t)m * prm.wcap;
@@ -385,7 +417,7 @@ traverse_kernel(const TraverseParams prm) {
                     return window_visit_order((int)a - woff[ha], nlv[ha], spv[ha]) <
                            window_visit_order((int)b2 - woff[ha], nlv[ha], spv[ha]);
                 };
-                cta_bucket_place_and_rank<ValT>(kA, Wm, slot, bkey, bval, cnt, lay.nbuckets, scale, s_scratch,
+                cta_bucket_place_and_rank<ValT, ValT>(kA, Wm, slot, bkey, bval, cnt, lay.nbuckets, scale, s_scratch,
                                                 rk, tie_less);
             } else {
                 // many equal priorities: stable radix sort of the windows laid out in visiting order
@@ -398,46 +430,57 @@ traverse_kernel(const TraverseParams prm) {
                     }
                 }
                 __syncthreads();
-                cta_radix_sort<ValT, ValT, true>(fb_k0, fb_v0, fb_k1, fb_v1, Wm, reinterpret_cast<ValT *>(cnt),
+                cta_radix_sort<ValT, ValT, true>(fb_k0, fb_v0, fb_k1, fb_v1, Wm, cnt,
                                                  s_scratch, rk);
             }
             DCI_PHASE_MARK(2)
         }
 
         // ---- 3. promotion iteration and lane of every point; lane-0 promotions listed
-        for (int p0 = 0; p0 < n; p0 += blockDim.x) {
-            const int p = p0 + tid;
-            const bool live = p < n;
-            uint32_t best = 0xFFFFFFFFu;
-            if (live) {
-                const PosT *pp = spos + (size_t)(lo + p) * I;
-                for (int m = 0; m < L; ++m) {
-                    const ValT *rk = rank + (size_t)m * prm.wcap;
-                    uint32_t mx = 0u;
-                    for (int h0 = 0; h0 < S; h0 += 4) {
-                        uint32_t yv[4];
+        // Each thread carries kPromoPoints points through all simple indices so that
+        // the per-index constants stay in registers and the position loads of one
+        // index are independent of each other.
+        for (int p0 = 0; p0 < n; p0 += kPromoPoints * blockDim.x) {
+            uint32_t best[kPromoPoints];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u)
-                            yv[u] = (h0 + u < S) ? (uint32_t)__ldg(pp + m * S + h0 + u) : 0u;
+            for (int j = 0; j < kPromoPoints; ++j) best[j] = 0xFFFFFFFFu;
+            for (int m = 0; m < L; ++m) {
+                const ValT *rkm = rank + (size_t)m * prm.wcap;
+                uint32_t mx[kPromoPoints];
 #pragma unroll
-                        for (int u = 0; u < 4; ++u) {
-                            if (h0 + u < S) {
-                                const int2 cb = s_cb[m * S + h0 + u];
-                                const uint32_t x = yv[u] + (uint32_t)cb.x;       // position relative to window 0
-                                const uint32_t g = prm.divT.div(x);
-                                const uint32_t t = x - g * (uint32_t)T;
-                                const uint32_t r = (uint32_t)rk[cb.y + g];
-                                mx = max(mx, (r << prm.tshift) | t);
-                            }
-                        }
+                for (int j = 0; j < kPromoPoints; ++j) mx[j] = 0u;
+                for (int h = 0; h < S; ++h) {
+                    const int i = m * S + h;
+                    const int2 cb = s_cb[i];
+                    const PosT *row = spos + (size_t)i * N + lo;
+                    const ValT *rkb = rkm + cb.y;
+                    uint32_t y[kPromoPoints];
+#pragma unroll
+                    for (int j = 0; j < kPromoPoints; ++j) {
+                        const int p = p0 + j * blockDim.x + tid;
+                        y[j] = p < n ? (uint32_t)__ldg(row + p) : 0u;
                     }
-                    if ((mx >> prm.tshift) < (best >> prm.tshift)) best = mx;   // ties keep the lower composite
+#pragma unroll
+                    for (int j = 0; j < kPromoPoints; ++j) {
+                        const uint32_t x = y[j] + (uint32_t)cb.x;        // position relative to window 0
+                        const uint32_t g = prm.divT.div(x);
+                        const uint32_t t = x - g * (uint32_t)T;
+                        mx[j] = max(mx[j], ((uint32_t)rkb[g] << prm.tshift) | t);
+                    }
                 }
-                kenc[p] = best;
+#pragma unroll
+                for (int j = 0; j < kPromoPoints; ++j)
+                    if ((mx[j] >> prm.tshift) < (best[j] >> prm.tshift)) best[j] = mx[j];   // ties keep the lower composite
             }
-            const bool is0 = live && (best & tmask) == 0u;
-            const int slot0 = warp_append_slot(is0, &s_count[0]);
-            if (is0) list[slot0] = (ValT)(best >> prm.tshift);
+#pragma unroll
+            for (int j = 0; j < kPromoPoints; ++j) {
+                const int p = p0 + j * blockDim.x + tid;
+                const bool live = p < n;
+                if (live) kenc[p] = best[j];
+                const bool is0 = live && (best[j] & tmask) == 0u;
+                const int slot0 = warp_append_slot(is0, &s_count[0]);
+                if (is0) list[slot0] = (ValT)(best[j] >> prm.tshift);
+            }
         }
         __syncthreads();
 
@@ -506,11 +549,17 @@ traverse_kernel(const TraverseParams prm) {
         DCI_PHASE_MARK(4)
         // ---- 5. distances of the promoted points and the partition's top-k
         CtaTopK topk;
-        topk.init(topk_bufs, &s_count[0], &s_thresh, s_sel, s_res, prm.topk_cap, prm.knn);
+        topk.init(topk_bufs, &s_count[0], &s_thresh, s_sel, s_res, prm.topk_cap, prm.kpart);
         for (int base = 0; base < ncand; base += blockDim.x) {
             uint64_t key = kEmptySlot;
             const int j = base + tid;
-            if (SMEM && prm.vec4) {
+            if (prm.vec8) {
+                if (j < ncand) {
+                    const long long gid = lo + (long long)list[j];
+                    const float d = dist_sequential_v8(prm.data + (size_t)gid * dim, qvec, dim);
+                    key = ((uint64_t)__float_as_uint(d) << 32) | (uint32_t)gid;
+                }
+            } else if (SMEM && prm.vec4) {
                 const long long gid = lo + (long long)list[j < ncand ? j : 0];
                 const float d = dist_rows_tiled(prm.data, gid, qvec, dim, tiles + warp * (32 * kDistStride));
                 if (j < ncand) key = ((uint64_t)__float_as_uint(d) << 32) | (uint32_t)gid;
@@ -524,9 +573,9 @@ traverse_kernel(const TraverseParams prm) {
             DCI_PHASE_MARK(6)
         }
         topk.finish();
-        uint64_t *out = prm.part_topk + ((size_t)ql * prm.num_parts + b) * prm.knn;
+        uint64_t *out = prm.part_topk + ((size_t)ql * prm.num_parts + b) * prm.kpart;
         const uint64_t *res = topk.result();
-        for (int j = tid; j < prm.knn; j += blockDim.x) out[j] = res[j];
+        for (int j = tid; j < prm.kpart; j += blockDim.x) out[j] = res[j];
         __syncthreads();
         DCI_PHASE_MARK(6)
         if (prm.phase_cycles && tid == 0) atomicAdd((unsigned long long *)&prm.phase_cycles[15], 1ull);
@@ -534,37 +583,42 @@ traverse_kernel(const TraverseParams prm) {
 #undef DCI_PHASE_MARK
 }
 
-// Final top-k of one query over the per-partition lists (replaces
-// get_top_candidates, src/dci_cuda_kernel.cu:691-701).  One CTA per query.
-__global__ void merge_partitions_kernel(const uint64_t *__restrict__ part_topk, int num_parts,
-                                        int knn, int topk_cap, int q0, int *__restrict__ out_ids,
-                                        float *__restrict__ out_dists) {
+// Final top-k of a query over its per-partition lists (replaces
+// get_top_candidates, src/dci_cuda_kernel.cu:691-701).  CTAs loop over queries.
+// The selection buffers are dynamic shared memory, or -- for large k -- the
+// CTA's slab of `gbufs` (2 * topk_cap entries each).
+__global__ void merge_partitions_kernel(const uint64_t *__restrict__ part_topk, int num_parts, int kpart,
+                                        int knn, int topk_cap, int q0, int nq, uint64_t *gbufs,
+                                        int *__restrict__ out_ids, float *__restrict__ out_dists) {
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     __shared__ int s_count;
     __shared__ uint64_t s_thresh;
     __shared__ uint32_t s_sel[2][256];
     __shared__ uint32_t s_res[4];
-    const int ql = blockIdx.x;
-    const uint64_t *in = part_topk + (size_t)ql * num_parts * knn;
-    const long long total = (long long)num_parts * knn;
-    CtaTopK topk;
-    topk.init(reinterpret_cast<uint64_t *>(dyn_smem), &s_count, &s_thresh, s_sel, s_res, topk_cap, knn);
-    for (long long base = 0; base < total; base += blockDim.x) {
-        const long long j = base + threadIdx.x;
-        topk.offer(j < total ? in[j] : kEmptySlot);
-    }
-    topk.finish();
-    const uint64_t *buf = topk.result();
-    for (int j = threadIdx.x; j < knn; j += blockDim.x) {
-        const uint64_t key = buf[j];
-        const size_t o = (size_t)(q0 + ql) * knn + j;
-        if (key == kEmptySlot) {
-            out_ids[o] = -1;
-            out_dists[o] = __int_as_float(0x7F800000);
-        } else {
-            out_ids[o] = (int)(uint32_t)key;
-            out_dists[o] = __uint_as_float((uint32_t)(key >> 32));
+    uint64_t *bufs = gbufs ? gbufs + (size_t)blockIdx.x * 2 * topk_cap : reinterpret_cast<uint64_t *>(dyn_smem);
+    const long long total = (long long)num_parts * kpart;
+    for (int ql = blockIdx.x; ql < nq; ql += gridDim.x) {
+        const uint64_t *in = part_topk + (size_t)ql * total;
+        CtaTopK topk;
+        topk.init(bufs, &s_count, &s_thresh, s_sel, s_res, topk_cap, knn);
+        for (long long base = 0; base < total; base += blockDim.x) {
+            const long long j = base + threadIdx.x;
+            topk.offer(j < total ? in[j] : kEmptySlot);
         }
+        topk.finish();
+        const uint64_t *buf = topk.result();
+        for (int j = threadIdx.x; j < knn; j += blockDim.x) {
+            const uint64_t key = buf[j];
+            const size_t o = (size_t)(q0 + ql) * knn + j;
+            if (key == kEmptySlot) {
+                out_ids[o] = -1;
+                out_dists[o] = __int_as_float(0x7F800000);
+            } else {
+                out_ids[o] = (int)(uint32_t)key;
+                out_dists[o] = __uint_as_float((uint32_t)(key >> 32));
+            }
+        }
+        __syncthreads();
     }
 }
 

@@ -88,7 +88,9 @@ int dci_b200_add(dci_b200_t *h, const float *d_data, int num_points, int block_s
  * passes them on every call).  blind != 0 returns DCI_B200_ERR_UNSUPPORTED
  * (the reference's blind path writes out of bounds).
  * d_ids: [num_queries][num_neighbours] int32, d_dists: same shape fp32.  Slots
- * beyond the number of promoted points hold id -1 and distance +inf. */
+ * beyond the number of promoted points hold id -1 and distance +inf.
+ * Any 1 <= num_neighbours <= num_points is accepted; above 1024 the selection
+ * buffers move from shared to global memory and the query is slower. */
 int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
                    int num_outer_iterations, int max_num_candidates, int blind,
                    int block_size, int thread_size, int *d_ids, float *d_dists, void *stream);

@@ -145,6 +145,28 @@ def test_wide_rank_path():
     _assert_same(ids, dists, oi, od, gs, os_, "wide-rank")
 
 
+def test_default_k_returns_every_point():
+    """num_neighbours = -1 means k = N (reference core.py:84-85): every point of every
+    partition is promoted (lane 0 cannot reach k) and the result is the full sorted list."""
+    rng = np.random.default_rng(8)
+    c = dict(data=cases.latent_linear(rng, 3000, 8, 16, 0.01), query=cases.latent_linear(rng, 5, 8, 16, 0.01),
+             L=2, S=3, P=3, T=10, k=3000, outer=5000, max_cand=None, proj=cases.unit_rows(rng, 6, 16))
+    g = _dci(c)
+    g.add(torch.from_numpy(c["data"]).cuda())
+    ids, dists = g.query(torch.from_numpy(c["query"]).cuda(), return_int_ids=True)      # default k
+    bi, bd = oracle.bruteforce(c["data"], c["query"], 3000)
+    assert np.array_equal(ids.cpu().numpy(), bi)
+    assert np.array_equal(dists.cpu().numpy().view(np.uint32), bd.view(np.uint32))
+
+
+def test_large_k_uses_global_selection_buffers():
+    rng = np.random.default_rng(9)
+    c = dict(data=cases.latent_linear(rng, 20000, 8, 16, 0.01), query=cases.latent_linear(rng, 3, 8, 16, 0.01),
+             L=2, S=3, P=2, T=10, k=15000, outer=5000, max_cand=None, proj=cases.unit_rows(rng, 6, 16))
+    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
+    _assert_same(ids, dists, oi, od, gs, os_, "large-k")
+
+
 def test_query_host_buffers_match_device_buffers():
     c = cases.example_config(n=1000, nq=40)
     g = _dci(c)
