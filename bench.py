@@ -42,12 +42,41 @@ CFG = dict(n_points=1_000_000, n_queries=10_000, dim=128, latent=32, noise=0.01,
 METRIC = "queries/sec at recall@10>=0.9 (1M x 128 fp32 synthetic, k=10, L=2, S=10, P=100, T=10)"
 
 
+# Other BASELINE.json configurations, for manual runs (--workload); the default bench line is configs[1].
+WORKLOADS = {
+    "configs1": dict(CFG),
+    # configs[2]: 1M x 960, uniform[0,1) rows scaled to unit length, L=3, S=12, max candidates 10000
+    "configs2": dict(n_points=1_000_000, n_queries=1_000, dim=960, kind="unit_uniform", k=10, L=3, S=12, P=100, T=10,
+                     outer=5000, max_cand=10000),
+    # configs[3], one of 8 shards: 10M/8+1 points of a 256-centre Gaussian mixture, dim 96
+    "configs3_shard": dict(n_points=1_250_001, n_queries=10_000, dim=96, kind="mixture", k=10, L=2, S=10, P=100, T=10,
+                           outer=5000),
+    # configs[4], one of 8 shards: 4M/8+1 points, dim 256 from a 64-d latent, k=100, S=15, 20000 outer iterations
+    "configs4_shard": dict(n_points=500_001, n_queries=2_000, dim=256, latent=64, noise=0.0, k=100, L=2, S=15, P=100,
+                           T=10, outer=20000),
+}
+
+
+WORKLOAD_LABEL = {"configs1": "configs[1]", "configs2": "configs[2]", "configs3_shard": "configs[3] (one of 8 shards)",
+                  "configs4_shard": "configs[4] (one of 8 shards)"}
+
+
 def make_data(seed, n, nq, cfg):
-    """rows = randn(n+nq, latent) @ randn(latent, dim) + noise*randn; the last nq rows are queries."""
+    """Seeded synthetic rows; the last nq rows are the queries.  Default kind: randn(., latent) @
+    randn(latent, dim) + noise * randn."""
     g = torch.Generator().manual_seed(seed)
-    a = torch.randn(cfg["latent"], cfg["dim"], generator=g)
-    z = torch.randn(n + nq, cfg["latent"], generator=g) @ a
-    z += cfg["noise"] * torch.randn(n + nq, cfg["dim"], generator=g)
+    kind = cfg.get("kind", "latent")
+    if kind == "unit_uniform":
+        z = torch.rand(n + nq, cfg["dim"], generator=g)
+        z /= z.norm(dim=1, keepdim=True)
+    elif kind == "mixture":
+        centres = 4.0 * torch.randn(256, cfg["dim"], generator=g)
+        z = centres[torch.randint(256, (n + nq,), generator=g)] + torch.randn(n + nq, cfg["dim"], generator=g)
+    else:
+        a = torch.randn(cfg["latent"], cfg["dim"], generator=g)
+        z = torch.randn(n + nq, cfg["latent"], generator=g) @ a
+        if cfg.get("noise"):
+            z += cfg["noise"] * torch.randn(n + nq, cfg["dim"], generator=g)
     return z[:n].contiguous(), z[n:].contiguous()
 
 
@@ -154,8 +183,12 @@ def bench_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    cfg = dict(CFG)
-    cfg["n_points"], cfg["n_queries"] = args.points, args.queries
+    cfg = dict(WORKLOADS[args.workload])
+    if args.points:
+        cfg["n_points"] = args.points
+    if args.queries:
+        cfg["n_queries"] = args.queries
+    mc = cfg.get("max_cand")
     # every rank draws the same queries (seed 1); rank r > 0 draws its own shard
     data_h, query_h = make_data(1, cfg["n_points"], cfg["n_queries"], cfg)
     if rank > 0:
@@ -177,7 +210,7 @@ def bench_ours(args):
     build_ms = e0.elapsed_time(e1)
 
     def step():
-        return engine.query(query, cfg["k"], cfg["outer"], return_int_ids=True)
+        return engine.query(query, cfg["k"], cfg["outer"], max_num_candidates=mc, return_int_ids=True)
 
     def barrier():
         torch.cuda.synchronize()
@@ -211,8 +244,9 @@ def bench_ours(args):
     q_pin = query_h.pin_memory()
     def e2e_step():
         if world == 1:
-            return engine.query_host(q_pin, cfg["k"], cfg["outer"])
-        a, d = engine.query(q_pin.to(dev, non_blocking=True), cfg["k"], cfg["outer"], return_int_ids=True)
+            return engine.query_host(q_pin, cfg["k"], cfg["outer"], max_num_candidates=mc)
+        a, d = engine.query(q_pin.to(dev, non_blocking=True), cfg["k"], cfg["outer"], max_num_candidates=mc,
+                            return_int_ids=True)
         return a.cpu(), d.cpu()
     e2e_step()
     barrier()
@@ -230,11 +264,11 @@ def bench_ours(args):
     if rank == 0:
         # roofline of the dominant kernel (traversal): algorithmic bytes from the work counters
         local_dci.enable_work_stats(False, phases=True)
-        local_dci.query(query, cfg["k"], cfg["outer"])
+        local_dci.query(query, cfg["k"], cfg["outer"], max_num_candidates=mc)
         torch.cuda.synchronize()
         phases = local_dci.get_phase_cycles()
         local_dci.enable_work_stats(True)
-        local_dci.query(query, cfg["k"], cfg["outer"])
+        local_dci.query(query, cfg["k"], cfg["outer"], max_num_candidates=mc)
         torch.cuda.synchronize()
         st = local_dci.get_work_stats(nq)
         local_dci.enable_work_stats(False)
@@ -243,7 +277,7 @@ def bench_ours(args):
         local_dci.enable_timing(True)
         tr, pj, mg, nl = [], [], [], 0
         for _ in range(max(3, args.steps)):
-            local_dci.query(query, cfg["k"], cfg["outer"])
+            local_dci.query(query, cfg["k"], cfg["outer"], max_num_candidates=mc)
             t = local_dci.get_timing()
             tr.append(t["traverse_ms"]); pj.append(t["project_ms"]); mg.append(t["merge_ms"]); nl = t["traverse_launches"]
         local_dci.enable_timing(False)
@@ -264,16 +298,18 @@ def bench_ours(args):
         nrec = min(1000, nq)
         rec = recall_at_k(ids[:nrec] if world == 1 else ids[:nrec], data, query[:nrec], cfg["k"]) if world == 1 else None
         cpu_port, cpu_brute = (None, None)
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and args.workload == "configs1":
             cpu_port, cpu_brute = cpu_baselines(local_dci, data_h, query_h, cfg)
         out = {
             "metric": METRIC, "value": value, "unit": "queries/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "configs[1]: %d points x dim %d per GPU, %d queries, k=%d, L=%d, S=%d, P=%d, T=%d, num_outer_iterations=%d"
-                                   % (cfg["n_points"], cfg["dim"], nq, cfg["k"], cfg["L"], cfg["S"], cfg["P"], cfg["T"], cfg["outer"]),
+            "config": {"workload": "%s: %d points x dim %d per GPU, %d queries, k=%d, L=%d, S=%d, P=%d, T=%d, num_outer_iterations=%d"
+                                   % (WORKLOAD_LABEL[args.workload],
+                                      cfg["n_points"], cfg["dim"], nq, cfg["k"], cfg["L"], cfg["S"], cfg["P"], cfg["T"], cfg["outer"]),
                        "points_total": world * cfg["n_points"], "queries_per_step": nq,
-                       "l2": "inputs larger than L2 (index 160 MB + data 512 MB per GPU)",
+                       "l2": "inputs larger than L2 (index %d MB + data %d MB per GPU)"
+                             % (cfg["n_points"] * cfg["L"] * cfg["S"] * 10 // 1_000_000, cfg["n_points"] * cfg["dim"] * 4 // 1_000_000),
                        "parallelism": "1 GPU" if world == 1 else "MDCI: %d shards, NCCL all-gather + device merge" % world,
                        "value_unit_note": "(query, shard) answers per second" if world > 1 else "queries per second"},
             "index_queries_per_s": nq / (ms_per_step * 1e-3),
@@ -294,8 +330,11 @@ def bench_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cfg = dict(CFG)
-    cfg["n_points"], cfg["n_queries"] = args.points, args.queries
+    cfg = dict(WORKLOADS[args.workload])
+    if args.points:
+        cfg["n_points"] = args.points
+    if args.queries:
+        cfg["n_queries"] = args.queries
     data_h, query_h = make_data(1, cfg["n_points"], cfg["n_queries"], cfg)
     base = {"impl": "reference", "metric": METRIC, "unit": "queries/s", "n_gpus": args.gpus, "steps": args.steps,
             "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
@@ -358,8 +397,9 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--points", type=int, default=CFG["n_points"])
-    ap.add_argument("--queries", type=int, default=CFG["n_queries"])
+    ap.add_argument("--workload", default="configs1", choices=sorted(WORKLOADS))
+    ap.add_argument("--points", type=int, default=0, help="override the workload's number of points (per GPU)")
+    ap.add_argument("--queries", type=int, default=0, help="override the workload's number of queries")
     ap.add_argument("--ref-queries", type=int, default=256, help="cap on the reference arm's queries per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

@@ -180,36 +180,31 @@ __device__ __forceinline__ int bucket_of(uint32_t key_bits, float scale, int las
 // Second half of the counting rank.  Precondition: every key w in [0, W) has
 // been dropped into bucket_of(key[w]) with slot[w] = its arrival number there
 // and cnt[b] = the size of bucket b (all <= kMaxBucket), cnt[nbuckets] = 0.
-// Moves the keys bucket by bucket into (bkey, bval), then gives every key its
-// rank in ascending (key, tie order): rank = start of its bucket + number of
-// smaller keys inside the bucket.  tie_less(a, b) orders two key indices whose
-// keys are equal.  rank_out[w] receives the rank.  Ends with a barrier.
+// Lists the key indices bucket by bucket in bval, then gives every key its rank
+// in ascending (key, tie order): rank = start of its bucket + number of smaller
+// keys inside the bucket.  tie_less(a, b) orders two key indices whose keys are
+// equal.  rank_out[w] receives the rank.  Ends with a barrier.
 template <typename ValT, typename CntT, typename TieLess>
 __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, int W, const uint8_t *slot,
-                                                          uint32_t *bkey, ValT *bval, CntT *cnt,
-                                                          int nbuckets, float scale, uint32_t *scratch,
-                                                          ValT *rank_out, TieLess tie_less) {
+                                                          ValT *bval, CntT *cnt, int nbuckets, float scale,
+                                                          uint32_t *scratch, ValT *rank_out, TieLess tie_less) {
     const int tid = threadIdx.x, last = nbuckets - 1;
     cta_exclusive_scan<CntT>(cnt, nbuckets + 1, scratch);    // cnt[b] = start of bucket b, cnt[nbuckets] = W
+    for (int w = tid; w < W; w += blockDim.x)
+        bval[(uint32_t)cnt[bucket_of(key[w], scale, last)] + (uint32_t)slot[w]] = (ValT)w;
+    __syncthreads();
     for (int w = tid; w < W; w += blockDim.x) {
         const uint32_t k = key[w];
-        const uint32_t pos = cnt[bucket_of(k, scale, last)] + (uint32_t)slot[w];
-        bkey[pos] = k;
-        bval[pos] = (ValT)w;
-    }
-    __syncthreads();
-    for (int pos = tid; pos < W; pos += blockDim.x) {
-        const uint32_t k = bkey[pos];
-        const uint32_t v = (uint32_t)bval[pos];
         const int b = bucket_of(k, scale, last);
         const uint32_t lo = cnt[b], hi = cnt[b + 1];
         uint32_t r = lo;
         for (uint32_t j = lo; j < hi; ++j) {
-            const uint32_t kj = bkey[j];
+            const uint32_t other = (uint32_t)bval[j];
+            const uint32_t kj = key[other];
             if (kj < k) ++r;
-            else if (kj == k && j != (uint32_t)pos && tie_less((uint32_t)bval[j], v)) ++r;
+            else if (kj == k && other != (uint32_t)w && tie_less(other, (uint32_t)w)) ++r;
         }
-        rank_out[v] = (ValT)r;
+        rank_out[w] = (ValT)r;
     }
     __syncthreads();
 }

@@ -147,7 +147,7 @@ int pick_buckets(dci_b200 *h, const dci::TraverseParams &prm, int nthreads, size
     for (int c = 0; c < 3; ++c) {
         const int nb = std::min(std::max(choices[c], 64), 1 << 20);
         const auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_global ? 0 : prm.topk_cap, prm.L,
-                                                         prm.wcap, prm.ppb, nb, true);
+                                                         prm.wcap, prm.ppb, nb, prm.vec4 && !prm.vec8);
         if (lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin) return nb;
     }
     return std::min(std::max(prm.wcap / 2, 64), 16384);
@@ -161,7 +161,8 @@ int launch_traverse(dci_b200 *h, dci::TraverseParams prm, int nthreads, cudaStre
     const size_t static_smem = fa.sharedSizeBytes;
     prm.nbuckets = pick_buckets<ValT>(h, prm, nthreads, static_smem);
     const int cap_smem = prm.topk_global ? 0 : prm.topk_cap;
-    auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, cap_smem, prm.L, prm.wcap, prm.ppb, prm.nbuckets, true);
+    auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, cap_smem, prm.L, prm.wcap, prm.ppb, prm.nbuckets,
+                                               prm.vec4 && !prm.vec8);
     if (lay.fixed_bytes + static_smem > h->smem_optin)
         return fail(DCI_B200_ERR_UNSUPPORTED, "dim=%d with k=%d needs %zu bytes of shared memory per CTA, more than the device offers",
                     prm.dim, prm.knn, lay.fixed_bytes + static_smem);
@@ -583,7 +584,8 @@ int query_noalloc_impl(dci_b200 *h, dci::TraverseParams prm, int nthreads, unsig
     DCI_CUDA(cudaFuncGetAttributes(&fa, dci::traverse_kernel<ValT, PosT, true>));
     const size_t static_smem = fa.sharedSizeBytes;
     prm.nbuckets = pick_buckets<ValT>(h, prm, nthreads, static_smem);
-    auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, prm.nbuckets, true);
+    auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, prm.nbuckets,
+                                               prm.vec4 && !prm.vec8);
     if (lay.fixed_bytes + static_smem > h->smem_optin)
         return fail(DCI_B200_ERR_UNSUPPORTED, "dim=%d needs more shared memory per CTA than the device offers", prm.dim);
     const bool smem = lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin;

@@ -76,7 +76,7 @@ struct TraverseLayout {
     size_t cnt_bytes, qvec_bytes, fixed_bytes;
     int nbuckets;
     // "big" region (shared or global): [rank table per composite][union]
-    //   union, ordering view : kA u32[wcap] | bkey u32[wcap] | bval ValT[wcap] | slot u8[wcap]
+    //   union, ordering view : kA u32[wcap] | bval ValT[wcap] | slot u8[wcap]
     //   union, point view    : kenc u32[ppb] | ... | list ValT[ppb] at list_off
     //   union, distance view : top-k 2 x u64[topk_cap] | staging tiles | ... | list (kept)
     size_t rank_bytes, wk_bytes, wv_bytes, ws_bytes, point_bytes, list_bytes, topk_bytes, tile_bytes,
@@ -85,7 +85,7 @@ struct TraverseLayout {
     size_t fallback_bytes;
     __host__ __device__ static size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
     __host__ __device__ static TraverseLayout make(int nthreads, int dim, int topk_cap, int L,
-                                                   int wcap, int ppb, int nbuckets, bool smem) {
+                                                   int wcap, int ppb, int nbuckets, bool tiles) {
         TraverseLayout l;
         const size_t radix_hist = (size_t)256 * (nthreads / 32) * sizeof(ValT);
         l.nbuckets = nbuckets;
@@ -100,11 +100,11 @@ struct TraverseLayout {
         l.point_bytes = align16((size_t)ppb * 4);
         l.list_bytes = align16((size_t)ppb * sizeof(ValT));
         l.topk_bytes = align16((size_t)topk_cap * 8) * 2;
-        // staging tiles only pay off in shared memory
-        l.tile_bytes = smem ? (size_t)(nthreads / 32) * 32 * kDistStride * 4 : 0;
+        // staging tiles: shared-memory variant only, and only when rows cannot be read sector by sector
+        l.tile_bytes = tiles ? (size_t)(nthreads / 32) * 32 * kDistStride * 4 : 0;
         const size_t need = l.topk_bytes + l.tile_bytes;
         l.list_off = l.point_bytes > need ? l.point_bytes : need;
-        const size_t sort_total = 2 * l.wk_bytes + l.wv_bytes + l.ws_bytes;
+        const size_t sort_total = l.wk_bytes + l.wv_bytes + l.ws_bytes;
         const size_t point_total = l.list_off + l.list_bytes;
         l.big_bytes = l.rank_bytes + (sort_total > point_total ? sort_total : point_total);
         l.fallback_bytes = 2 * l.wk_bytes + 2 * l.wv_bytes;
@@ -271,7 +271,7 @@ traverse_kernel(const TraverseParams prm) {
     const int L = prm.L, S = prm.S, T = prm.T, I = L * S, N = prm.N, dim = prm.dim;
     const TraverseLayout<ValT> lay =
         TraverseLayout<ValT>::make(blockDim.x, dim, prm.topk_global ? 0 : prm.topk_cap, L, prm.wcap, prm.ppb,
-                                   prm.nbuckets, SMEM);
+                                   prm.nbuckets, SMEM && prm.vec4 && !prm.vec8);
     ValT *cnt = reinterpret_cast<ValT *>(dyn_smem);                    // bucket counters / radix histogram
     float *qvec = reinterpret_cast<float *>(dyn_smem + lay.cnt_bytes);
     unsigned char *slab = prm.gscratch + (size_t)blockIdx.x * prm.gscratch_per_cta;
@@ -280,9 +280,8 @@ traverse_kernel(const TraverseParams prm) {
     unsigned char *uni = big + lay.rank_bytes;
     // ordering view of the union region
     uint32_t *kA = reinterpret_cast<uint32_t *>(uni);
-    uint32_t *bkey = reinterpret_cast<uint32_t *>(uni + lay.wk_bytes);
-    ValT *bval = reinterpret_cast<ValT *>(uni + 2 * lay.wk_bytes);
-    uint8_t *slot = reinterpret_cast<uint8_t *>(uni + 2 * lay.wk_bytes + lay.wv_bytes);
+    ValT *bval = reinterpret_cast<ValT *>(uni + lay.wk_bytes);
+    uint8_t *slot = reinterpret_cast<uint8_t *>(uni + lay.wk_bytes + lay.wv_bytes);
     // radix-sort fallback buffers (global)
     uint32_t *fb_k0 = reinterpret_cast<uint32_t *>(slab);
     uint32_t *fb_k1 = reinterpret_cast<uint32_t *>(slab + lay.wk_bytes);
@@ -417,7 +416,7 @@ traverse_kernel(const TraverseParams prm) {
                     return window_visit_order((int)a - woff[ha], nlv[ha], spv[ha]) <
                            window_visit_order((int)b2 - woff[ha], nlv[ha], spv[ha]);
                 };
-                cta_bucket_place_and_rank<ValT, ValT>(kA, Wm, slot, bkey, bval, cnt, lay.nbuckets, scale, s_scratch,
+                cta_bucket_place_and_rank<ValT, ValT>(kA, Wm, slot, bval, cnt, lay.nbuckets, scale, s_scratch,
                                                 rk, tie_less);
             } else {
                 // many equal priorities: stable radix sort of the windows laid out in visiting order
