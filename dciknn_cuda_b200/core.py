@@ -268,8 +268,9 @@ class DCI(object):
         (needs enable_work_stats(..., phases=True))."""
         buf = (C.c_longlong * 16)()
         _capi.check(_capi.lib().dci_b200_get_phase_cycles(self._live(), buf))
-        names = ["load_search", "priorities", "ordering", "promotion", "stop_candidates", "distance", "topk"]
-        out = {n: int(buf[i]) for i, n in enumerate(names)}
+        names = ["load_search", "priorities", "ordering_rank", "promotion", "stop_candidates", "distance", "topk",
+                 None, "ordering_scan", "ordering_place", "counter_reset"]
+        out = {n: int(buf[i]) for i, n in enumerate(names) if n}
         out["work_items"] = int(buf[15])
         return out
 

@@ -6,7 +6,10 @@
 // inverse permutation pos[L*S][N]: pos[i][p] = position of point p inside its
 // partition's sorted segment of simple index i (16-bit when partitions hold
 // fewer than 65 536 points), which lets a query look a point's window up
-// directly instead of scattering over index entries.
+// directly instead of scattering over index entries.  A third copy of the keys,
+// keysT, holds every segment "stride-T transposed": the key at sorted position
+// y = j*T + r sits at r*(n/T) + min(r, n%T) + j, so that the keys at positions
+// r, r+T, r+2T, ... -- the window starts of one query -- are contiguous.
 // Equal keys are ordered by id (the input order), which the reference leaves
 // unspecified.
 #pragma once
@@ -33,7 +36,8 @@ template <typename ValT, bool SMEM>
 __global__ void __launch_bounds__(1024)
 build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_indices, int ppb,
                       int num_parts, float *__restrict__ skeys, int *__restrict__ sids,
-                      ValT *__restrict__ spos, unsigned char *gscratch, size_t gscratch_per_cta) {
+                      ValT *__restrict__ spos, float *__restrict__ skeysT, int T,
+                      unsigned char *gscratch, size_t gscratch_per_cta) {
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     __shared__ uint32_t warp_tot[40];
     const BuildLayout<ValT> lay = BuildLayout<ValT>::make(blockDim.x, ppb);
@@ -57,7 +61,10 @@ build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_in
         }
         __syncthreads();
         cta_radix_sort<ValT, ValT, false>(kA, vA, kB, vB, n, hist, warp_tot, (ValT *)nullptr);
+        const int qn = n / T, rem = n % T;
         for (int x = threadIdx.x; x < n; x += blockDim.x) {
+            const int r = x % T, j = x / T;
+            skeysT[row + r * qn + min(r, rem) + j] = ordered_to_float(kA[x]);
             skeys[row + x] = ordered_to_float(kA[x]);
             sids[row + x] = (int)(lo + vA[x]);
             spos[row + vA[x]] = (ValT)x;

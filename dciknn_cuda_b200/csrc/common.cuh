@@ -82,6 +82,66 @@ __device__ __forceinline__ uint32_t cta_exclusive_scan_u32(uint32_t *a, int n, u
     return cta_exclusive_scan<uint32_t>(a, n, scratch);
 }
 
+// Exclusive scan of 16-bit counters in shared memory, eight at a time (128-bit
+// accesses).  `a` must be 16-byte aligned and allocated (and zero) up to the
+// next multiple of 8 entries beyond n.  Ends with a barrier.
+__device__ __forceinline__ void cta_exclusive_scan_u16x8(uint16_t *a, int n, uint32_t *scratch) {
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5, nw = blockDim.x >> 5;
+    const int n8 = (n + 7) >> 3;                                   // groups of 8 entries
+    const int per = (n8 + blockDim.x - 1) / blockDim.x;            // groups per thread
+    const int g0 = min(tid * per, n8), g1 = min(g0 + per, n8);
+    uint4 *v = reinterpret_cast<uint4 *>(a);
+    uint32_t sum = 0;
+    for (int g = g0; g < g1; ++g) {
+        const uint4 x = v[g];
+        sum += (x.x & 0xFFFFu) + (x.x >> 16) + (x.y & 0xFFFFu) + (x.y >> 16) + (x.z & 0xFFFFu) + (x.z >> 16) +
+               (x.w & 0xFFFFu) + (x.w >> 16);
+    }
+    uint32_t inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t t = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+        if (lane >= o) inc += t;
+    }
+    if (lane == 31) scratch[w] = inc;
+    __syncthreads();
+    if (w == 0) {
+        const uint32_t t = lane < nw ? scratch[lane] : 0;
+        uint32_t i2 = t;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t u = __shfl_up_sync(0xFFFFFFFFu, i2, o);
+            if (lane >= o) i2 += u;
+        }
+        scratch[lane] = i2 - t;
+    }
+    __syncthreads();
+    uint32_t base = scratch[w] + inc - sum;
+    for (int g = g0; g < g1; ++g) {
+        const uint4 x = v[g];
+        uint4 y;
+        uint32_t c;
+        c = x.x & 0xFFFFu; y.x = base; base += c; c = x.x >> 16; y.x |= base << 16; base += c;
+        c = x.y & 0xFFFFu; y.y = base; base += c; c = x.y >> 16; y.y |= base << 16; base += c;
+        c = x.z & 0xFFFFu; y.z = base; base += c; c = x.z >> 16; y.z |= base << 16; base += c;
+        c = x.w & 0xFFFFu; y.w = base; base += c; c = x.w >> 16; y.w |= base << 16; base += c;
+        v[g] = y;
+    }
+    __syncthreads();
+}
+__device__ __forceinline__ void cta_scan_counters(uint16_t *a, int n, uint32_t *scratch) {
+    cta_exclusive_scan_u16x8(a, n, scratch);
+}
+__device__ __forceinline__ void cta_scan_counters(uint32_t *a, int n, uint32_t *scratch) {
+    cta_exclusive_scan<uint32_t>(a, n, scratch);
+}
+
+// Zeroes `bytes` (a multiple of 16) of 16-byte aligned shared memory.  No barrier.
+__device__ __forceinline__ void cta_zero16(void *p, size_t bytes) {
+    uint4 *v = reinterpret_cast<uint4 *>(p);
+    for (size_t i = threadIdx.x; i < (bytes >> 4); i += blockDim.x) v[i] = make_uint4(0u, 0u, 0u, 0u);
+}
+
 // Bucket counters are 32-bit, or 16-bit packed two to a word (counts must then
 // stay below 65 536, which holds whenever the number of keys does).  arrive()
 // adds one to bucket b and returns the previous count.
@@ -184,25 +244,34 @@ __device__ __forceinline__ int bucket_of(uint32_t key_bits, float scale, int las
 // in ascending (key, tie order): rank = start of its bucket + number of smaller
 // keys inside the bucket.  tie_less(a, b) orders two key indices whose keys are
 // equal.  rank_out[w] receives the rank.  Ends with a barrier.
-template <typename ValT, typename CntT, typename TieLess>
+template <typename ValT, typename CntT, typename TieLess, typename Mark>
 __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, int W, const uint8_t *slot,
                                                           ValT *bval, CntT *cnt, int nbuckets, float scale,
-                                                          uint32_t *scratch, ValT *rank_out, TieLess tie_less) {
+                                                          uint32_t *scratch, ValT *rank_out, TieLess tie_less,
+                                                          Mark mark) {
     const int tid = threadIdx.x, last = nbuckets - 1;
-    cta_exclusive_scan<CntT>(cnt, nbuckets + 1, scratch);    // cnt[b] = start of bucket b, cnt[nbuckets] = W
+    cta_scan_counters(cnt, nbuckets + 1, scratch);           // cnt[b] = start of bucket b, cnt[nbuckets] = W
+    mark(8);
     for (int w = tid; w < W; w += blockDim.x)
         bval[(uint32_t)cnt[bucket_of(key[w], scale, last)] + (uint32_t)slot[w]] = (ValT)w;
     __syncthreads();
+    mark(9);
     for (int w = tid; w < W; w += blockDim.x) {
         const uint32_t k = key[w];
         const int b = bucket_of(k, scale, last);
         const uint32_t lo = cnt[b], hi = cnt[b + 1];
         uint32_t r = lo;
-        for (uint32_t j = lo; j < hi; ++j) {
-            const uint32_t other = (uint32_t)bval[j];
-            const uint32_t kj = key[other];
-            if (kj < k) ++r;
-            else if (kj == k && other != (uint32_t)w && tie_less(other, (uint32_t)w)) ++r;
+        for (uint32_t j0 = lo; j0 < hi; j0 += 4) {      // four bucket mates at a time: independent loads
+            uint32_t other[4], kj[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) other[u] = j0 + u < hi ? (uint32_t)bval[j0 + u] : (uint32_t)w;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) kj[u] = key[other[u]];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (kj[u] < k) ++r;
+                else if (kj[u] == k && other[u] != (uint32_t)w && tie_less(other[u], (uint32_t)w)) ++r;
+            }
         }
         rank_out[w] = (ValT)r;
     }

@@ -73,7 +73,7 @@ struct dci_b200 {
     int num_points = 0, P = 0, T = 0, ppb = 0, num_parts = 0;
     const float *d_data = nullptr;       // borrowed
     float *d_proj = nullptr;             // [L*S][dim]
-    Buf keys, ids, pos;                  // [L*S][N] sorted index and inverse positions
+    Buf keys, ids, pos, keysT;           // [L*S][N] sorted index, inverse positions, stride-T keys
     Buf tmp_keys, qproj, part_topk, scratch, merge_scratch, stats, phases, hq, hids, hdists;
     int stats_on = 0, stats_nq = 0, phases_valid = 0;
     int timing_on = 0;
@@ -124,13 +124,15 @@ int launch_build(dci_b200 *h, const float *d_unsorted, cudaStream_t st) {
         int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + 1024), 2048 / nthreads));
         const unsigned grid = (unsigned)std::min<long long>(nseg, (long long)h->sm_count * per_sm);
         kern<<<grid, nthreads, dyn, st>>>(d_unsorted, h->num_points, I, h->ppb, h->num_parts,
-                                          (float *)h->keys.p, (int *)h->ids.p, (ValT *)h->pos.p, nullptr, 0);
+                                          (float *)h->keys.p, (int *)h->ids.p, (ValT *)h->pos.p, (float *)h->keysT.p, h->T,
+                                          nullptr, 0);
     } else {
         auto kern = dci::build_segments_kernel<ValT, false>;
         const unsigned grid = (unsigned)std::min<long long>(nseg, (long long)h->sm_count * (2048 / nthreads));
         DCI_CUDA(h->scratch.ensure(lay.buf_bytes * grid));
         kern<<<grid, nthreads, lay.hist_bytes, st>>>(d_unsorted, h->num_points, I, h->ppb, h->num_parts,
                                                      (float *)h->keys.p, (int *)h->ids.p, (ValT *)h->pos.p,
+                                                     (float *)h->keysT.p, h->T,
                                                      (unsigned char *)h->scratch.p, lay.buf_bytes);
     }
     h->launches++;
@@ -242,7 +244,7 @@ int dci_b200_destroy(dci_b200_t *h) {
     if (!h) return 0;
     DeviceGuard g(h->device);
     cudaDeviceSynchronize();
-    Buf *bufs[] = {&h->keys, &h->ids, &h->pos, &h->tmp_keys, &h->qproj, &h->part_topk, &h->scratch, &h->merge_scratch, &h->stats, &h->phases,
+    Buf *bufs[] = {&h->keys, &h->ids, &h->pos, &h->keysT, &h->tmp_keys, &h->qproj, &h->part_topk, &h->scratch, &h->merge_scratch, &h->stats, &h->phases,
                    &h->hq, &h->hids, &h->hdists};
     for (Buf *b : bufs) b->release();
     if (h->d_proj) cudaFree(h->d_proj);
@@ -296,6 +298,7 @@ int dci_b200_add(dci_b200_t *h, const float *d_data, int num_points, int block_s
     const size_t n_entries = (size_t)I * num_points;
     DCI_CUDA(h->keys.ensure(n_entries * sizeof(float)));
     DCI_CUDA(h->ids.ensure(n_entries * sizeof(int)));
+    DCI_CUDA(h->keysT.ensure(n_entries * sizeof(float)));
     DCI_CUDA(h->pos.ensure(n_entries * (ppb <= 65535 ? sizeof(uint16_t) : sizeof(uint32_t))));
     DCI_CUDA(h->tmp_keys.ensure(n_entries * sizeof(float)));
     h->num_points = num_points; h->P = block_size; h->T = thread_size; h->ppb = ppb; h->num_parts = num_parts;
@@ -338,7 +341,8 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
 
     dci::TraverseParams prm;
     memset(&prm, 0, sizeof(prm));
-    prm.skeys = (const float *)h->keys.p; prm.sids = (const int *)h->ids.p; prm.spos = h->pos.p; prm.data = h->d_data;
+    prm.skeys = (const float *)h->keys.p; prm.skeysT = (const float *)h->keysT.p; prm.sids = (const int *)h->ids.p;
+    prm.spos = h->pos.p; prm.data = h->d_data;
     prm.qproj = (const float *)h->qproj.p; prm.query = d_query;
     prm.N = h->num_points; prm.dim = h->dim; prm.L = h->L; prm.S = h->S; prm.P = h->P; prm.T = h->T;
     prm.ppb = h->ppb; prm.num_parts = h->num_parts; prm.nq_total = num_queries;
@@ -437,7 +441,7 @@ int dci_b200_clear(dci_b200_t *h) {
     if (int rc = check_handle(h)) return rc;
     DeviceGuard g(h->device);
     DCI_CUDA(cudaDeviceSynchronize());
-    h->keys.release(); h->ids.release(); h->pos.release(); h->tmp_keys.release();
+    h->keys.release(); h->ids.release(); h->pos.release(); h->keysT.release(); h->tmp_keys.release();
     h->num_points = 0; h->d_data = nullptr; h->P = h->T = h->ppb = h->num_parts = 0;
     return 0;
 }
@@ -657,7 +661,8 @@ extern "C" int dci_b200_query_noalloc(dci_b200_t *h, const float *d_query, int n
 
     dci::TraverseParams prm;
     memset(&prm, 0, sizeof(prm));
-    prm.skeys = (const float *)h->keys.p; prm.sids = (const int *)h->ids.p; prm.spos = h->pos.p; prm.data = h->d_data;
+    prm.skeys = (const float *)h->keys.p; prm.skeysT = (const float *)h->keysT.p; prm.sids = (const int *)h->ids.p;
+    prm.spos = h->pos.p; prm.data = h->d_data;
     prm.qproj = qproj; prm.query = d_query;
     prm.N = h->num_points; prm.dim = h->dim; prm.L = h->L; prm.S = h->S; prm.P = h->P; prm.T = h->T;
     prm.ppb = h->ppb; prm.num_parts = h->num_parts; prm.nq_total = num_queries;

@@ -40,6 +40,7 @@ namespace dci {
 
 struct TraverseParams {
     const float *skeys;        // [I][N] sorted keys
+    const float *skeysT;       // [I][N] the same keys, every segment stride-T transposed
     const int *sids;           // [I][N] point ids
     const void *spos;          // [I][N] position of each point in its sorted segment (u16 or u32)
     const float *data;         // [N][dim]
@@ -89,7 +90,7 @@ struct TraverseLayout {
         TraverseLayout l;
         const size_t radix_hist = (size_t)256 * (nthreads / 32) * sizeof(ValT);
         l.nbuckets = nbuckets;
-        const size_t bucket_cnt = sizeof(ValT) * (size_t)(nbuckets + 2);
+        const size_t bucket_cnt = sizeof(ValT) * (size_t)(nbuckets + 16);   // zero padding for vector scans
         l.cnt_bytes = align16(radix_hist > bucket_cnt ? radix_hist : bucket_cnt);
         l.qvec_bytes = align16((size_t)dim * 4);
         l.fixed_bytes = l.cnt_bytes + l.qvec_bytes;
@@ -258,6 +259,7 @@ traverse_kernel(const TraverseParams prm) {
     __shared__ int s_cnt[kMaxIndices];       // number of windows
     __shared__ int s_sp[kMaxIndices];        // 1: the only right window precedes the left ones
     __shared__ int2 s_cb[kMaxIndices];       // x: c (window 0 starts at -c), y: first window id in its composite
+    __shared__ int s_kt[kMaxIndices];        // index into the stride-T keys of window 0's start (may be -1)
     __shared__ float s_qp[kMaxIndices];      // projected query
     __shared__ int s_woff[kMaxIndices + 64]; // per composite: S+1 window offsets
     __shared__ uint32_t s_scratch[40];
@@ -343,7 +345,10 @@ traverse_kernel(const TraverseParams prm) {
                 s_nl[i] = nl;
                 s_cnt[i] = nl + nr;
                 s_sp[i] = (s == n - 1 && nr > 0) ? 1 : 0;
-                s_cb[i].x = nl * T - s - 1;
+                const int c = nl * T - s - 1;                  // 0 <= c < T
+                s_cb[i].x = c;
+                const int r0 = c ? T - c : 0;                  // residue class of every window start
+                s_kt[i] = r0 * (n / T) + min(r0, n % T) - (c ? 1 : 0);
                 // no window priority exceeds the distance to the farthest key
                 const float far = fmaxf(fabsf(keys[0] - qv), fabsf(keys[n - 1] - qv));
                 atomicMax(&s_maxpri, __float_as_uint(far));
@@ -372,9 +377,11 @@ traverse_kernel(const TraverseParams prm) {
         for (int m = 0; m < L; ++m) {
             const int *woff = s_woff + m * (S + 1);
             const int Wm = woff[S];
-            for (int i = tid; i < lay.nbuckets + 2; i += blockDim.x) cnt[i] = 0;
+            cta_zero16(cnt, lay.cnt_bytes);
             __syncthreads();
+            DCI_PHASE_MARK(10)
             const int gmax = prm.wcap / S;                  // no simple index has more windows than this
+            const int last_t = ((n - 1) % T) * (n / T) + min((n - 1) % T, n % T) + (n - 1) / T;
             for (int h0 = 0; h0 < S; h0 += 4) {
                 for (int g = tid; g < gmax; g += blockDim.x) {
                     float kv[4];
@@ -383,8 +390,11 @@ traverse_kernel(const TraverseParams prm) {
                         const int i = m * S + h0 + u;
                         kv[u] = 0.0f;
                         if (h0 + u < S && g < s_cnt[i]) {
-                            const int kp = min(max(g * T - s_cb[i].x, 0), n - 1);
-                            kv[u] = __ldg(prm.skeys + (size_t)i * N + lo + kp);
+                            // window starts are contiguous in the stride-T layout; the two clamped
+                            // cases read the segment's first / last key
+                            const int start = g * T - s_cb[i].x;
+                            const int at = start < 0 ? 0 : (start >= n ? last_t : s_kt[i] + g);
+                            kv[u] = __ldg(prm.skeysT + (size_t)i * N + lo + at);
                         }
                     }
 #pragma unroll
@@ -416,8 +426,9 @@ traverse_kernel(const TraverseParams prm) {
                     return window_visit_order((int)a - woff[ha], nlv[ha], spv[ha]) <
                            window_visit_order((int)b2 - woff[ha], nlv[ha], spv[ha]);
                 };
+                auto mark = [&](int slot_) { DCI_PHASE_MARK(slot_) };
                 cta_bucket_place_and_rank<ValT, ValT>(kA, Wm, slot, bval, cnt, lay.nbuckets, scale, s_scratch,
-                                                rk, tie_less);
+                                                      rk, tie_less, mark);
             } else {
                 // many equal priorities: stable radix sort of the windows laid out in visiting order
                 for (int h = 0; h < S; ++h) {

@@ -131,10 +131,11 @@ int dci_b200_get_work_stats(dci_b200_t *h, long long *h_out, long long capacity_
 
 /* With bit 1 of enable_work_stats set the traversal kernel also sums, over all work
  * items of the last query, the SM cycles one CTA spent in each of its phases:
- * h_out (16 entries): [0] query load + split search, [1] window priorities,
- * [2] window ordering, [3] promotion iterations, [4] stop rule + candidate
- * list (+ the counters above), [5] distances, [6] top-k; [15] = number of work
- * items.  Synchronous. */
+ * h_out (16 entries): [0] query load + split search, [1] window priorities +
+ * bucket counts, [2] window ranking inside buckets (or the radix-sort fallback),
+ * [3] promotion iterations, [4] stop rule + candidate list (+ the counters
+ * above), [5] distances, [6] top-k, [8] bucket scan, [9] bucket placement,
+ * [10] counter reset; [15] = number of work items.  Synchronous. */
 int dci_b200_get_phase_cycles(dci_b200_t *h, long long *h_out);
 
 /* Number of kernels this library launched on behalf of this handle so far. */
