@@ -274,6 +274,13 @@ class DCI(object):
         out["work_items"] = int(buf[15])
         return out
 
+    def set_projection(self, mode):
+        """'exact' (default; fixed fp32 summation order) or 'tf32x3' (tcgen05 tensor cores)."""
+        rc = _capi.lib().dci_b200_set_projection(self._live(), {"exact": 0, "tf32x3": 1}[mode])
+        if rc == _capi.ERR_STATE:
+            raise RuntimeError(_capi.lib().dci_b200_last_error().decode())
+        _capi.check(rc)
+
     def enable_timing(self, on=True):
         _capi.check(_capi.lib().dci_b200_enable_timing(self._live(), 1 if on else 0))
 

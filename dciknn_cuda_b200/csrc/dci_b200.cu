@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "directions.cuh"
 #include "project.cuh"
+#include "project_tf32.cuh"
 #include "traverse.cuh"
 
 namespace {
@@ -77,6 +78,8 @@ struct dci_b200 {
     Buf tmp_keys, qproj, part_topk, scratch, merge_scratch, stats, phases, hq, hids, hdists;
     int stats_on = 0, stats_nq = 0, phases_valid = 0;
     int timing_on = 0;
+    int projection_mode = 0;             // 0: exact fp32 FMA order, 1: tensor cores, 3xTF32
+    Buf errflag;
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
     float t_project = 0.f, t_traverse = 0.f, t_merge = 0.f;
     int t_traverse_launches = 0;
@@ -97,6 +100,22 @@ int launch_directions(dci_b200 *h, unsigned long long seed, cudaStream_t st) {
 int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cudaStream_t st) {
     if (n <= 0) return 0;
     const int I = h->L * h->S;
+    if (h->projection_mode == 1) {
+        DCI_CUDA(h->errflag.ensure(sizeof(int)));
+        DCI_CUDA(cudaMemsetAsync(h->errflag.p, 0, sizeof(int), st));
+        const unsigned tgrid = (unsigned)((n + dci::kTcPoints - 1) / dci::kTcPoints);
+        for (int i0 = 0; i0 < I; i0 += dci::kTcDirs) {
+            dci::project_tf32x3_kernel<<<tgrid, dci::kTcPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, i0, d_out,
+                                                                       (int *)h->errflag.p);
+            h->launches++;
+            DCI_CUDA(cudaGetLastError());
+        }
+        int flag = 0;      // this mode checks its bounded waits before going on
+        DCI_CUDA(cudaMemcpyAsync(&flag, h->errflag.p, sizeof(int), cudaMemcpyDeviceToHost, st));
+        DCI_CUDA(cudaStreamSynchronize(st));
+        if (flag) return fail(DCI_B200_ERR_CUDA, "tensor-core projection: a wait on the MMA barrier timed out");
+        return 0;
+    }
     const unsigned grid = (unsigned)((n + dci::kProjPoints - 1) / dci::kProjPoints);
     if (I <= 8)
         dci::project_exact_kernel<8><<<grid, dci::kProjPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
@@ -244,7 +263,7 @@ int dci_b200_destroy(dci_b200_t *h) {
     if (!h) return 0;
     DeviceGuard g(h->device);
     cudaDeviceSynchronize();
-    Buf *bufs[] = {&h->keys, &h->ids, &h->pos, &h->keysT, &h->tmp_keys, &h->qproj, &h->part_topk, &h->scratch, &h->merge_scratch, &h->stats, &h->phases,
+    Buf *bufs[] = {&h->keys, &h->ids, &h->pos, &h->keysT, &h->tmp_keys, &h->qproj, &h->part_topk, &h->scratch, &h->merge_scratch, &h->stats, &h->phases, &h->errflag,
                    &h->hq, &h->hids, &h->hdists};
     for (Buf *b : bufs) b->release();
     if (h->d_proj) cudaFree(h->d_proj);
@@ -506,6 +525,14 @@ int dci_b200_get_phase_cycles(dci_b200_t *h, long long *h_out) {
 }
 
 long long dci_b200_launch_count(dci_b200_t *h) { return h ? h->launches : 0; }
+
+int dci_b200_set_projection(dci_b200_t *h, int mode) {
+    if (int rc = check_handle(h)) return rc;
+    if (mode != 0 && mode != 1) return fail(DCI_B200_ERR_ARG, "projection mode must be 0 (exact) or 1 (tensor cores, 3xTF32)");
+    if (h->num_points > 0) return fail(DCI_B200_ERR_STATE, "the projection mode cannot change while the index holds points; clear first");
+    h->projection_mode = mode;
+    return 0;
+}
 
 int dci_b200_enable_timing(dci_b200_t *h, int on) {
     if (int rc = check_handle(h)) return rc;

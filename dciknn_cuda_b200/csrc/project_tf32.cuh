@@ -1,0 +1,203 @@
+// Tensor-core projection: out[i][p] = <proj[i], x[p]> on the 5th-generation
+// tensor cores (tcgen05.mma, accumulator in tensor memory) with fp32 operands
+// split into two tf32 terms ("3xTF32": a*b ~= a_lo*b_hi + a_hi*b_lo + a_hi*b_hi).
+// An optional replacement for the exact kernel of project.cuh, i.e. for the
+// cublasSgemm calls of the reference (src/util_kernel.cu:45-80).  Keys differ
+// from the exact path by about 1e-6 * |x| (not bit-identical), so the exact
+// path stays the default and the one the parity tests pin.
+//
+// One CTA of 128 threads computes a tile of 128 points x 32 directions (the
+// L*S <= 32 directions are zero padded).  Per 32-wide slice of the coordinate
+// axis the threads stage the hi and lo parts of the points (A) and directions
+// (B) in shared memory in the K-major no-swizzle canonical layout of the UMMA
+// shared-memory descriptor (core matrices of 8 rows x 16 bytes, 128 bytes each;
+// the next 16 bytes along K are 128 bytes further, the next 8 rows 1024 bytes
+// further), one thread issues 4 x 3 MMAs of shape 128 x 32 x 8 and commits them
+// to an mbarrier, and all threads wait for it before restaging.  Several CTAs
+// share an SM (40 KB of shared memory and 32 tensor-memory columns each), which
+// overlaps one CTA's loads with another's MMAs.  The epilogue reads the 128 x 32
+// accumulator with tcgen05.ld (lane = point, column = direction) and writes
+// coalesced rows of `out`.  Every wait is bounded; on a time-out the kernel
+// raises *error, skips its stores, frees its tensor memory and returns.
+#pragma once
+#include "common.cuh"
+
+namespace dci {
+
+constexpr int kTcPoints = 128;     // M of the MMA tile (points)
+constexpr int kTcDirs = 32;        // N of the MMA tile (directions, zero padded)
+constexpr int kTcK = 32;           // coordinates staged per step
+constexpr uint32_t kTcWaitLimit = 1u << 22;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+// K-major, no swizzle: start address, leading (K) byte offset 128, stride (8-row) byte offset 1024,
+// descriptor version 1 (bits 46-47), layout type 0.
+__device__ __forceinline__ uint64_t umma_desc_kmajor(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128u >> 4) << 16) | ((uint64_t)(1024u >> 4) << 32) |
+           (1ull << 46);
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n"
+        :
+        : "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+__device__ __forceinline__ void split_tf32(float a, float &hi, float &lo) {
+    hi = __uint_as_float(__float_as_uint(a) & 0xFFFFE000u);      // the 19 bits a tf32 operand keeps
+    lo = __uint_as_float(__float_as_uint(__fsub_rn(a, hi)) & 0xFFFFE000u);
+}
+
+__global__ void __launch_bounds__(kTcPoints)
+project_tf32x3_kernel(const float *__restrict__ x, long long n, int dim, const float *__restrict__ proj,
+                      int num_indices, int i0, float *__restrict__ out, int *error) {
+    __shared__ __align__(1024) float a_hi[kTcPoints * kTcK];
+    __shared__ __align__(1024) float a_lo[kTcPoints * kTcK];
+    __shared__ __align__(1024) float b_hi[kTcDirs * kTcK];
+    __shared__ __align__(1024) float b_lo[kTcDirs * kTcK];
+    __shared__ __align__(8) unsigned long long mbar;
+    __shared__ uint32_t tmem_slot;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const long long p0 = (long long)blockIdx.x * kTcPoints;
+    const bool vec_ok = (dim % 4 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                        ((reinterpret_cast<uintptr_t>(proj) & 15) == 0);
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"((uint32_t)kTcDirs));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&mbar)));
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = tmem_slot;
+
+    // instruction descriptor: D = f32, A = B = tf32, both K-major, N = 32, M = 128
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kTcDirs >> 3) << 17) |
+                           ((uint32_t)(kTcPoints >> 4) << 24);
+    uint32_t parity = 0, accumulate = 0;
+    int failed = 0;
+
+    for (int k0 = 0; k0 < dim && !failed; k0 += kTcK) {
+        // stage A: 128 rows x 8 sixteen-byte pieces; 8 consecutive threads read one row's 128 bytes
+        for (int f = tid; f < kTcPoints * (kTcK / 4); f += kTcPoints) {
+            const int row = f >> 3, piece = f & 7, col = k0 + piece * 4;
+            const long long p = p0 + row;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p < n) {
+                const float *src = x + p * dim + col;
+                if (vec_ok && col + 3 < dim) {
+                    v = __ldg(reinterpret_cast<const float4 *>(src));
+                } else {
+                    if (col < dim) v.x = __ldg(src);
+                    if (col + 1 < dim) v.y = __ldg(src + 1);
+                    if (col + 2 < dim) v.z = __ldg(src + 2);
+                    if (col + 3 < dim) v.w = __ldg(src + 3);
+                }
+            }
+            float4 h, l;
+            split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+            const int off = (row >> 3) * 256 + piece * 32 + (row & 7) * 4;     // in floats
+            *reinterpret_cast<float4 *>(a_hi + off) = h;
+            *reinterpret_cast<float4 *>(a_lo + off) = l;
+        }
+        // stage B: 32 rows (directions i0 .. i0+31, zero beyond num_indices) x 8 pieces
+        for (int f = tid; f < kTcDirs * (kTcK / 4); f += kTcPoints) {
+            const int row = f >> 3, piece = f & 7, col = k0 + piece * 4;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (i0 + row < num_indices) {
+                const float *src = proj + (size_t)(i0 + row) * dim + col;
+                if (vec_ok && col + 3 < dim) {
+                    v = __ldg(reinterpret_cast<const float4 *>(src));
+                } else {
+                    if (col < dim) v.x = __ldg(src);
+                    if (col + 1 < dim) v.y = __ldg(src + 1);
+                    if (col + 2 < dim) v.z = __ldg(src + 2);
+                    if (col + 3 < dim) v.w = __ldg(src + 3);
+                }
+            }
+            float4 h, l;
+            split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+            const int off = (row >> 3) * 256 + piece * 32 + (row & 7) * 4;
+            *reinterpret_cast<float4 *>(b_hi + off) = h;
+            *reinterpret_cast<float4 *>(b_lo + off) = l;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic-proxy stores -> tensor-core reads
+        __syncthreads();
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t ah = smem_u32(a_hi), al = smem_u32(a_lo), bh = smem_u32(b_hi), bl = smem_u32(b_lo);
+#pragma unroll
+            for (int kk = 0; kk < kTcK / 8; ++kk) {          // one MMA covers 8 coordinates = 2 pieces = 256 bytes
+                const uint32_t step = kk * 256;
+                umma_tf32(tmem_d, umma_desc_kmajor(al + step), umma_desc_kmajor(bh + step), idesc, accumulate);
+                accumulate = 1;
+                umma_tf32(tmem_d, umma_desc_kmajor(ah + step), umma_desc_kmajor(bl + step), idesc, 1u);
+                umma_tf32(tmem_d, umma_desc_kmajor(ah + step), umma_desc_kmajor(bh + step), idesc, 1u);
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                             smem_u32(&mbar))
+                         : "memory");
+        }
+        // wait until the MMAs have read the staged tiles (bounded)
+        uint32_t done = 0;
+        for (uint32_t spin = 0; spin < kTcWaitLimit && !done; ++spin) {
+            asm volatile(
+                "{\n\t"
+                ".reg .pred p;\n\t"
+                "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                "selp.b32 %0, 1, 0, p;\n\t"
+                "}\n"
+                : "=r"(done)
+                : "r"(smem_u32(&mbar)), "r"(parity)
+                : "memory");
+        }
+        parity ^= 1u;
+        failed = __syncthreads_or(done ? 0 : 1);
+    }
+
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (!failed) {
+        // lane (= point) quarter of this warp, 32 columns (= directions) per thread
+        uint32_t r[32];
+        const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const long long p = p0 + tid;
+        if (p < n) {
+#pragma unroll
+            for (int c = 0; c < kTcDirs; ++c)
+                if (i0 + c < num_indices) out[(size_t)(i0 + c) * n + p] = __uint_as_float(r[c]);
+        }
+    } else if (tid == 0) {
+        atomicExch(error, 1);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)kTcDirs));
+    }
+}
+
+}  // namespace dci

@@ -141,6 +141,17 @@ int dci_b200_get_phase_cycles(dci_b200_t *h, long long *h_out);
 /* Number of kernels this library launched on behalf of this handle so far. */
 long long dci_b200_launch_count(dci_b200_t *h);
 
+/* How data and queries are projected on the directions (replaces the
+ * cublasSgemm calls of src/util_kernel.cu:45-80).  0 (default): exact fp32, one
+ * fused multiply-add per term in ascending coordinate order -- the path every
+ * parity test pins.  1: 5th-generation tensor cores (tcgen05.mma, fp32 operands
+ * split into two tf32 terms, "3xTF32"); keys then differ from mode 0 by about
+ * 1e-6 * |x|, which can move a point across a window boundary, so results are
+ * not guaranteed identical to mode 0.  Mode 1 synchronises the stream after
+ * each projection to check its bounded waits.  Rejected while the index holds
+ * points (data and queries must be projected the same way). */
+int dci_b200_set_projection(dci_b200_t *h, int mode);
+
 /* When enabled, every later query brackets its kernels with CUDA events on the
  * caller's stream and synchronises after each batch (so it is for measurement,
  * not production).  get_timing returns, for the last query, milliseconds spent
