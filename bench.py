@@ -197,17 +197,27 @@ def bench_ours(args):
     query = query_h.to(dev)
     if world == 1:
         engine = DCI(cfg["dim"], cfg["L"], cfg["S"], cfg["P"], cfg["T"], local, seed=2024)
+        engine.set_projection(args.projection)
         local_dci = engine
         adder = lambda: engine.add(data)
     else:
         engine = MDCI(cfg["dim"], cfg["L"], cfg["S"], cfg["P"], cfg["T"], process_group=dist.group.WORLD,
                       seeds=[2024 + r for r in range(world)])
         local_dci = engine.dcis[0]
+        local_dci.set_projection(args.projection)
         adder = lambda: engine.add_local(data, cfg["n_points"] + 1)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(); adder(); e1.record(); torch.cuda.synchronize()
     build_ms = e0.elapsed_time(e1)
+    # projection of the indexed points alone (it is part of build_ms): HBM-bound, 4*dim bytes in and
+    # 4*L*S bytes out per point
+    proj_ms = []
+    for _ in range(4):
+        e0.record(); local_dci.project(data); e1.record(); torch.cuda.synchronize()
+        proj_ms.append(e0.elapsed_time(e1))
+    proj_ms = min(proj_ms[1:])
+    proj_bytes = cfg["n_points"] * 4 * (cfg["dim"] + cfg["L"] * cfg["S"])
 
     def step():
         return engine.query(query, cfg["k"], cfg["outer"], max_num_candidates=mc, return_int_ids=True)
@@ -314,6 +324,7 @@ def bench_ours(args):
                        "value_unit_note": "(query, shard) answers per second" if world > 1 else "queries per second"},
             "index_queries_per_s": nq / (ms_per_step * 1e-3),
             "build_ms": build_ms, "recall_at_10": rec,
+            "projection": {"mode": args.projection, "data_ms": proj_ms, "gbps": proj_bytes / (proj_ms * 1e-3) / 1e9},
             "e2e": {"value": e2e_value, "unit": "queries/s", "h2d_bytes_per_step": nq * cfg["dim"] * 4,
                     "d2h_bytes_per_step": nq * cfg["k"] * (4 + id_bytes)},
             "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
@@ -402,6 +413,8 @@ def main():
     ap.add_argument("--queries", type=int, default=0, help="override the workload's number of queries")
     ap.add_argument("--ref-queries", type=int, default=256, help="cap on the reference arm's queries per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--projection", default="exact", choices=["exact", "tf32x3"],
+                    help="exact fp32 projection (default) or the tcgen05 3xTF32 kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)
     if args.impl == "reference":
