@@ -57,6 +57,11 @@ WORKLOADS = {
 }
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one traversal launch from an ncu capture
+# (profiles/traverse_kernel_configs1.md).  The index and the rows are read about once per launch and
+# everything else hits L2, so the figure does not grow with the number of queries.
+NCU_DRAM_BYTES_PER_LAUNCH = {"configs1": 733_723_000}
+
 WORKLOAD_LABEL = {"configs1": "configs[1]", "configs2": "configs[2]", "configs3_shard": "configs[3] (one of 8 shards)",
                   "configs4_shard": "configs[4] (one of 8 shards)"}
 
@@ -208,6 +213,8 @@ def bench_ours(args):
         adder = lambda: engine.add_local(data, cfg["n_points"] + 1)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    adder(); torch.cuda.synchronize()            # first add also allocates the index buffers
+    local_dci.clear(); local_dci.set_projection(args.projection)
     e0.record(); adder(); e1.record(); torch.cuda.synchronize()
     build_ms = e0.elapsed_time(e1)
     # projection of the indexed points alone (it is part of build_ms): HBM-bound, 4*dim bytes in and
@@ -301,7 +308,7 @@ def bench_ours(args):
         achieved = algo_bytes / max(nl, 1) / (tr_ms * 1e-3) / 1e9
         roofline = {"bound": "hbm", "kernel": "traverse_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
                     "frac": achieved / peak, "peak_source": "measured" if peaks else "fallback",
-                    "traffic": None, "algorithmic_bytes_per_launch": algo_bytes // max(nl, 1),
+                    "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload), "algorithmic_bytes_per_launch": algo_bytes // max(nl, 1),
                     "launch_ms": tr_ms, "project_ms": statistics.mean(pj), "merge_ms": statistics.mean(mg),
                     "entries_per_query": entries / nq, "candidates_per_query": cands / nq,
                     "phase_cycles_per_work_item": {k: v / max(phases["work_items"], 1) for k, v in phases.items() if k != "work_items"}}

@@ -465,7 +465,8 @@ int dci_b200_clear(dci_b200_t *h) {
     if (int rc = check_handle(h)) return rc;
     DeviceGuard g(h->device);
     DCI_CUDA(cudaDeviceSynchronize());
-    h->keys.release(); h->ids.release(); h->pos.release(); h->keysT.release(); h->tmp_keys.release();
+    // the index buffers are kept for the next add (add / query / clear cycles are the
+    // reference's typical use, example.py:75-82); destroy returns them
     h->num_points = 0; h->d_data = nullptr; h->P = h->T = h->ppb = h->num_parts = 0;
     return 0;
 }

@@ -103,7 +103,8 @@ int dci_b200_query_host(dci_b200_t *h, const float *h_query, int num_queries, in
 
 /* Replace dci_clear / dci_reset (include/dci.h:77-80, src/dci_cuda_kernel.cu:
  * 878-891): clear drops the indexed points and keeps the directions; reset also
- * draws new directions from `seed`.  Synchronous. */
+ * draws new directions from `seed`.  Synchronous.  The device buffers of the
+ * index are kept for the next add and returned by dci_b200_destroy. */
 int dci_b200_clear(dci_b200_t *h);
 int dci_b200_reset(dci_b200_t *h, unsigned long long seed);
 
