@@ -429,4 +429,27 @@ struct CtaTopK {
     }
 };
 
+// State of one streaming top-k kept in shared memory, so that several of them
+// can be driven from fully unrolled code without per-object registers.
+struct TopKSlot {
+    unsigned long long thresh;
+    int count;
+    int half;       // which half of its buffer pair currently holds the entries
+};
+
+__device__ __forceinline__ CtaTopK topk_slot_open(TopKSlot *s, uint64_t *bufs, uint32_t (*sel)[256], uint32_t *res,
+                                                  int cap, int k) {
+    CtaTopK t;
+    t.buf = bufs + (size_t)s->half * cap;
+    t.other = bufs + (size_t)(1 - s->half) * cap;
+    t.count = &s->count;
+    t.thresh = reinterpret_cast<uint64_t *>(&s->thresh);
+    t.sel = sel; t.res = res; t.cap = cap; t.k = k;
+    return t;
+}
+__device__ __forceinline__ void topk_slot_close(TopKSlot *s, const CtaTopK &t, const uint64_t *bufs) {
+    if (threadIdx.x == 0) s->half = (t.buf == bufs) ? 0 : 1;
+    __syncthreads();
+}
+
 }  // namespace dci

@@ -181,9 +181,8 @@ int pick_buckets(dci_b200 *h, const dci::TraverseParams &prm, int nthreads, size
 
 template <typename ValT, typename PosT>
 int launch_traverse(dci_b200 *h, dci::TraverseParams prm, int nthreads, cudaStream_t st) {
-    const long long nwork = (long long)prm.nq * prm.num_parts;
     cudaFuncAttributes fa;
-    DCI_CUDA(cudaFuncGetAttributes(&fa, dci::traverse_kernel<ValT, PosT, true>));
+    DCI_CUDA(cudaFuncGetAttributes(&fa, dci::traverse_kernel<ValT, PosT, true, true>));
     const size_t static_smem = fa.sharedSizeBytes;
     prm.nbuckets = pick_buckets<ValT>(h, prm, nthreads, static_smem);
     const int cap_smem = prm.topk_global ? 0 : prm.topk_cap;
@@ -195,19 +194,34 @@ int launch_traverse(dci_b200 *h, dci::TraverseParams prm, int nthreads, cudaStre
     const bool smem = lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin;
     if (!smem) lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, cap_smem, prm.L, prm.wcap, prm.ppb, prm.nbuckets, false);
     const size_t dyn = smem ? lay.fixed_bytes + lay.big_bytes : lay.fixed_bytes;
+    // queries per CTA pass: the dense distance pass needs, per query, a pair of selection buffers
+    // and the query vector inside the shared "big" region
+    // ... and pays off when work items are exhaustive: lane 0 of a partition sees about ppb / T
+    // promotions, so a quota well above that (with an iteration cap beyond the last window) is never met
+    prm.qbatch = 1;
+    const bool likely_exhaustive = (long long)prm.max_cand * prm.T * 2 > 3ll * prm.ppb && prm.outer_s >= prm.wcap;
+    if (smem && prm.vec8 && !prm.topk_global && likely_exhaustive) {
+        const size_t per_q = dci::TraverseLayout<ValT>::align16((size_t)prm.topk_cap * 8) * 2 + (size_t)prm.dim * 4 + 16;
+        prm.qbatch = (int)std::max<size_t>(1, std::min<size_t>(dci::kMaxQBatch, lay.big_bytes / per_q));
+    }
     prm.topk_global_off = lay.fallback_bytes + (smem ? 0 : lay.big_bytes);
     const size_t per_cta = prm.topk_global_off + (prm.topk_global ? (size_t)prm.topk_cap * 16 : 0);
     const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));
+    const long long nwork = (long long)((prm.nq + prm.qbatch - 1) / prm.qbatch) * prm.num_parts;
     const unsigned grid = (unsigned)std::min<long long>(nwork, (long long)h->sm_count * per_sm);
     DCI_CUDA(h->scratch.ensure(per_cta * grid));
     prm.gscratch = (unsigned char *)h->scratch.p;
     prm.gscratch_per_cta = per_cta;
-    if (smem) {
-        auto kern = dci::traverse_kernel<ValT, PosT, true>;
+    if (smem && prm.qbatch > 1) {
+        auto kern = dci::traverse_kernel<ValT, PosT, true, true>;
+        DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+        kern<<<grid, nthreads, dyn, st>>>(prm);
+    } else if (smem) {
+        auto kern = dci::traverse_kernel<ValT, PosT, true, false>;
         DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
         kern<<<grid, nthreads, dyn, st>>>(prm);
     } else {
-        auto kern = dci::traverse_kernel<ValT, PosT, false>;
+        auto kern = dci::traverse_kernel<ValT, PosT, false, false>;
         DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
         kern<<<grid, nthreads, dyn, st>>>(prm);
     }
@@ -618,7 +632,7 @@ template <typename ValT, typename PosT>
 int query_noalloc_impl(dci_b200 *h, dci::TraverseParams prm, int nthreads, unsigned char *scratch, size_t avail,
                        int num_queries, int *d_ids, float *d_dists, cudaStream_t st) {
     cudaFuncAttributes fa;
-    DCI_CUDA(cudaFuncGetAttributes(&fa, dci::traverse_kernel<ValT, PosT, true>));
+    DCI_CUDA(cudaFuncGetAttributes(&fa, dci::traverse_kernel<ValT, PosT, true, true>));
     const size_t static_smem = fa.sharedSizeBytes;
     prm.nbuckets = pick_buckets<ValT>(h, prm, nthreads, static_smem);
     auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, prm.nbuckets,
@@ -643,14 +657,14 @@ int query_noalloc_impl(dci_b200 *h, dci::TraverseParams prm, int nthreads, unsig
     prm.part_topk = (uint64_t *)(scratch + slabs);
     const int merge_threads = 256;
     const int merge_cap = next_pow2(prm.knn + merge_threads);
-    if (smem) DCI_CUDA(cudaFuncSetAttribute(dci::traverse_kernel<ValT, PosT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-    else DCI_CUDA(cudaFuncSetAttribute(dci::traverse_kernel<ValT, PosT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    if (smem) DCI_CUDA(cudaFuncSetAttribute(dci::traverse_kernel<ValT, PosT, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    else DCI_CUDA(cudaFuncSetAttribute(dci::traverse_kernel<ValT, PosT, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     for (int q0 = 0; q0 < num_queries; q0 += batch) {
         prm.q0 = q0;
         prm.nq = std::min(batch, num_queries - q0);
         const unsigned grid = (unsigned)std::min<long long>((long long)prm.nq * prm.num_parts, max_grid);
-        if (smem) dci::traverse_kernel<ValT, PosT, true><<<grid, nthreads, dyn, st>>>(prm);
-        else dci::traverse_kernel<ValT, PosT, false><<<grid, nthreads, dyn, st>>>(prm);
+        if (smem) dci::traverse_kernel<ValT, PosT, true, false><<<grid, nthreads, dyn, st>>>(prm);
+        else dci::traverse_kernel<ValT, PosT, false, false><<<grid, nthreads, dyn, st>>>(prm);
         h->launches++;
         DCI_CUDA(cudaGetLastError());
         dci::merge_partitions_kernel<<<prm.nq, merge_threads, (size_t)merge_cap * 16, st>>>(

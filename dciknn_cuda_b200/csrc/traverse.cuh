@@ -64,9 +64,11 @@ struct TraverseParams {
     int tshift;                // bits that hold the lane in an encoded promotion
     int vec4;                  // rows of data/query can be read as float4
     int vec8;                  // rows of data start on 32-byte boundaries: one full sector per load
+    int qbatch;                // queries of one partition a CTA takes together (1..kMaxQBatch)
     FastDiv divT;
 };
 
+constexpr int kMaxQBatch = 4;                  // queries whose exhaustive distance phases share row loads
 constexpr int kPromoPoints = 5;                // points a thread carries through the promotion phase
 constexpr int kDistChunk = 16;                 // floats of a row staged per step of the distance phase
 constexpr int kDistStride = kDistChunk + 4;    // padded row stride of the staging tile (floats)
@@ -250,7 +252,10 @@ __device__ __forceinline__ int window_visit_order(int g, int nl, int sp) {
     return g >= nl ? (sp ? 0 : g) : (nl - 1 - g + sp);
 }
 
-template <typename ValT, typename PosT, bool SMEM>
+// BATCH: compile the query-group path (Q > 1 with the dense distance pass).  The host picks it
+// when the configuration makes exhaustive work items likely; without it the kernel is the plain
+// one-query-per-pass loop.
+template <typename ValT, typename PosT, bool SMEM, bool BATCH>
 __global__ void __launch_bounds__(1024, 1)
 traverse_kernel(const TraverseParams prm) {
     extern __shared__ __align__(16) unsigned char dyn_smem[];
@@ -268,6 +273,8 @@ traverse_kernel(const TraverseParams prm) {
     __shared__ uint32_t s_maxpri;
     __shared__ int s_count[2];
     __shared__ uint64_t s_thresh;
+    __shared__ TopKSlot s_slot[kMaxQBatch];  // dense distance phase: one top-k per deferred query
+    __shared__ int s_dense[kMaxQBatch];      // local query numbers deferred to the dense phase
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     const int L = prm.L, S = prm.S, T = prm.T, I = L * S, N = prm.N, dim = prm.dim;
@@ -299,7 +306,12 @@ traverse_kernel(const TraverseParams prm) {
     const PosT *spos = reinterpret_cast<const PosT *>(prm.spos);
 
     const uint32_t tmask = (1u << prm.tshift) - 1u;
-    const long long nwork = (long long)prm.nq * prm.num_parts;
+    // A CTA takes Q consecutive queries of one partition together.  Queries whose traversal
+    // promotes every point of the partition (the exhaustive case of the reference's stop rule) are
+    // deferred and their distances computed in one pass that loads each row once for all of them.
+    const int Q = BATCH ? (prm.qbatch > 0 ? prm.qbatch : 1) : 1;
+    const int ngroups = (prm.nq + Q - 1) / Q;
+    const long long nwork = (long long)ngroups * prm.num_parts;
     long long t_last = 0;
 #define DCI_PHASE_MARK(slot_)                                                             \
     if (prm.phase_cycles && tid == 0) {                                                   \
@@ -309,9 +321,14 @@ traverse_kernel(const TraverseParams prm) {
     }
 
     for (long long wi = blockIdx.x; wi < nwork; wi += gridDim.x) {
-        const int b = (int)(wi / prm.nq), ql = (int)(wi % prm.nq), q = prm.q0 + ql;
-        const long long lo = (long long)b * prm.ppb;
-        const int n = (int)min((long long)prm.ppb, (long long)N - lo);
+      const int b = (int)(wi / ngroups), grp = (int)(wi % ngroups);
+      const long long lo = (long long)b * prm.ppb;
+      const int n = (int)min((long long)prm.ppb, (long long)N - lo);
+      int ndense = 0;
+      for (int jq = 0; jq < Q; ++jq) {
+        const int ql = grp * Q + jq;
+        if (ql >= prm.nq) break;
+        const int q = prm.q0 + ql;
         if (prm.phase_cycles && tid == 0) t_last = clock64();
 
         for (int i = tid; i < I; i += blockDim.x) s_qp[i] = prm.qproj[(size_t)i * prm.nq_total + q];
@@ -557,6 +574,15 @@ traverse_kernel(const TraverseParams prm) {
         }
 
         DCI_PHASE_MARK(4)
+        if (BATCH && Q > 1 && ncand == n) {   // every point promoted: distances in the shared pass below
+            if (tid == 0) {
+                s_dense[ndense] = ql;
+                if (prm.phase_cycles) atomicAdd((unsigned long long *)&prm.phase_cycles[15], 1ull);
+            }
+            ++ndense;
+            __syncthreads();
+            continue;
+        }
         // ---- 5. distances of the promoted points and the partition's top-k
         CtaTopK topk;
         topk.init(topk_bufs, &s_count[0], &s_thresh, s_sel, s_res, prm.topk_cap, prm.kpart);
@@ -589,6 +615,78 @@ traverse_kernel(const TraverseParams prm) {
         __syncthreads();
         DCI_PHASE_MARK(6)
         if (prm.phase_cycles && tid == 0) atomicAdd((unsigned long long *)&prm.phase_cycles[15], 1ull);
+      }   // queries of the group
+
+      // ---- 5'. dense distance pass for the deferred queries (host enables Q > 1 only with
+      // 256-bit row loads, shared-memory buffers and room for Q selection buffer pairs)
+      if (BATCH && ndense > 0) {
+        if (prm.phase_cycles && tid == 0) t_last = clock64();
+        const size_t tk_bytes = TraverseLayout<ValT>::align16((size_t)prm.topk_cap * 8) * 2;
+        float *dq = reinterpret_cast<float *>(big + (size_t)Q * tk_bytes);       // Q query vectors
+        for (int t = 0; t < ndense; ++t) {
+            const float *src = prm.query + (size_t)(prm.q0 + s_dense[t]) * dim;
+            for (int c = tid; c < dim; c += blockDim.x) dq[(size_t)t * dim + c] = src[c];
+            if (tid == 0) { s_slot[t].count = 0; s_slot[t].half = 0; s_slot[t].thresh = kEmptySlot; }
+        }
+        __syncthreads();
+        const int n8 = dim >> 3;
+        for (int base = 0; base < n; base += blockDim.x) {
+            const int r = base + tid;
+            const bool live = r < n;
+            float sq[kMaxQBatch];
+#pragma unroll
+            for (int t = 0; t < kMaxQBatch; ++t) sq[t] = 0.0f;
+            if (live) {
+                const float *row = prm.data + (size_t)(lo + r) * dim;
+                for (int c = 0; c < n8; ++c) {
+                    float a0, a1, a2, a3, a4, a5, a6, a7;
+                    asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                                 : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3), "=f"(a4), "=f"(a5), "=f"(a6), "=f"(a7)
+                                 : "l"(row + c * 8));
+#pragma unroll
+                    for (int t = 0; t < kMaxQBatch; ++t) {
+                        if (t < ndense) {
+                            const float4 b0 = *reinterpret_cast<const float4 *>(dq + (size_t)t * dim + c * 8);
+                            const float4 b1 = *reinterpret_cast<const float4 *>(dq + (size_t)t * dim + c * 8 + 4);
+                            float s_ = sq[t], d;
+                            d = __fsub_rn(a0, b0.x); s_ = __fmaf_rn(d, d, s_);
+                            d = __fsub_rn(a1, b0.y); s_ = __fmaf_rn(d, d, s_);
+                            d = __fsub_rn(a2, b0.z); s_ = __fmaf_rn(d, d, s_);
+                            d = __fsub_rn(a3, b0.w); s_ = __fmaf_rn(d, d, s_);
+                            d = __fsub_rn(a4, b1.x); s_ = __fmaf_rn(d, d, s_);
+                            d = __fsub_rn(a5, b1.y); s_ = __fmaf_rn(d, d, s_);
+                            d = __fsub_rn(a6, b1.z); s_ = __fmaf_rn(d, d, s_);
+                            d = __fsub_rn(a7, b1.w); s_ = __fmaf_rn(d, d, s_);
+                            sq[t] = s_;
+                        }
+                    }
+                }
+            }
+            DCI_PHASE_MARK(5)
+#pragma unroll
+            for (int t = 0; t < kMaxQBatch; ++t) {
+                if (t < ndense) {
+                    uint64_t *bufs = reinterpret_cast<uint64_t *>(big + (size_t)t * tk_bytes);
+                    CtaTopK topk = topk_slot_open(&s_slot[t], bufs, s_sel, s_res, prm.topk_cap, prm.kpart);
+                    const uint64_t key = live ? (((uint64_t)__float_as_uint(__fsqrt_rn(sq[t])) << 32) | (uint32_t)(lo + r))
+                                              : kEmptySlot;
+                    topk.offer(key);
+                    topk_slot_close(&s_slot[t], topk, bufs);
+                }
+            }
+            DCI_PHASE_MARK(6)
+        }
+        for (int t = 0; t < ndense; ++t) {
+            uint64_t *bufs = reinterpret_cast<uint64_t *>(big + (size_t)t * tk_bytes);
+            CtaTopK topk = topk_slot_open(&s_slot[t], bufs, s_sel, s_res, prm.topk_cap, prm.kpart);
+            topk.finish();
+            uint64_t *out = prm.part_topk + ((size_t)s_dense[t] * prm.num_parts + b) * prm.kpart;
+            const uint64_t *res = topk.result();
+            for (int j = tid; j < prm.kpart; j += blockDim.x) out[j] = res[j];
+            __syncthreads();
+        }
+        DCI_PHASE_MARK(6)
+      }
     }
 #undef DCI_PHASE_MARK
 }
