@@ -311,7 +311,9 @@ def bench_ours(args):
                     "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(args.workload), "algorithmic_bytes_per_launch": algo_bytes // max(nl, 1),
                     "launch_ms": tr_ms, "project_ms": statistics.mean(pj), "merge_ms": statistics.mean(mg),
                     "entries_per_query": entries / nq, "candidates_per_query": cands / nq,
-                    "phase_cycles_per_work_item": {k: v / max(phases["work_items"], 1) for k, v in phases.items() if k != "work_items"}}
+                    "phase_cycles_per_work_item": {k: v / max(phases["work_items"], 1) for k, v in phases.items()
+                                                   if k not in ("work_items", "queries_per_pass")},
+                    "queries_per_pass": phases["queries_per_pass"]}
         nrec = min(1000, nq)
         rec = recall_at_k(ids[:nrec] if world == 1 else ids[:nrec], data, query[:nrec], cfg["k"]) if world == 1 else None
         cpu_port, cpu_brute = (None, None)

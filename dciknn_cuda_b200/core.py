@@ -272,6 +272,7 @@ class DCI(object):
                  None, "ordering_scan", "ordering_place", "counter_reset"]
         out = {n: int(buf[i]) for i, n in enumerate(names) if n}
         out["work_items"] = int(buf[15])
+        out["queries_per_pass"] = int(buf[11])
         return out
 
     def set_projection(self, mode):

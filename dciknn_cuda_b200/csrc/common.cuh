@@ -422,6 +422,17 @@ struct CtaTopK {
         if (take) buf[sl] = key;
         __syncthreads();
     }
+    // offer() for rounds in which at most `producers` threads hold a key (the others pass
+    // kEmptySlot): the buffer only has to keep room for that many appends.
+    __device__ __forceinline__ void offer_from(uint64_t key, int producers) {
+        const int c = *count;
+        __syncthreads();
+        if (c > cap - producers) compact();
+        const bool take = key < *thresh;
+        const int sl = warp_append_slot(take, count);
+        if (take) buf[sl] = key;
+        __syncthreads();
+    }
     __device__ __forceinline__ void finish() {
         compact();
         for (int i = *count + threadIdx.x; i < k; i += blockDim.x) buf[i] = kEmptySlot;

@@ -78,6 +78,7 @@ struct dci_b200 {
     Buf tmp_keys, qproj, part_topk, scratch, merge_scratch, stats, phases, hq, hids, hdists;
     int stats_on = 0, stats_nq = 0, phases_valid = 0;
     int timing_on = 0;
+    int last_qbatch = 1;                 // queries per CTA pass of the last traversal launch
     int projection_mode = 0;             // 0: exact fp32 FMA order, 1: tensor cores, 3xTF32
     Buf errflag;
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -201,12 +202,14 @@ int launch_traverse(dci_b200 *h, dci::TraverseParams prm, int nthreads, cudaStre
     prm.qbatch = 1;
     const bool likely_exhaustive = (long long)prm.max_cand * prm.T * 2 > 3ll * prm.ppb && prm.outer_s >= prm.wcap;
     if (smem && prm.vec8 && !prm.topk_global && likely_exhaustive) {
-        const size_t per_q = dci::TraverseLayout<ValT>::align16((size_t)prm.topk_cap * 8) * 2 + (size_t)prm.dim * 4 + 16;
+        prm.dense_cap = next_pow2(prm.kpart + nthreads / 4);
+        const size_t per_q = (size_t)prm.dense_cap * 16 + (size_t)prm.dim * 4 + 16;
         prm.qbatch = (int)std::max<size_t>(1, std::min<size_t>(dci::kMaxQBatch, lay.big_bytes / per_q));
     }
     prm.topk_global_off = lay.fallback_bytes + (smem ? 0 : lay.big_bytes);
     const size_t per_cta = prm.topk_global_off + (prm.topk_global ? (size_t)prm.topk_cap * 16 : 0);
     const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));
+    h->last_qbatch = prm.qbatch;
     const long long nwork = (long long)((prm.nq + prm.qbatch - 1) / prm.qbatch) * prm.num_parts;
     const unsigned grid = (unsigned)std::min<long long>(nwork, (long long)h->sm_count * per_sm);
     DCI_CUDA(h->scratch.ensure(per_cta * grid));
@@ -541,6 +544,7 @@ int dci_b200_get_phase_cycles(dci_b200_t *h, long long *h_out) {
     DeviceGuard g(h->device);
     DCI_CUDA(cudaDeviceSynchronize());
     DCI_CUDA(cudaMemcpy(h_out, h->phases.p, sizeof(long long) * 16, cudaMemcpyDeviceToHost));
+    h_out[11] = h->last_qbatch;
     return 0;
 }
 

@@ -65,10 +65,11 @@ struct TraverseParams {
     int vec4;                  // rows of data/query can be read as float4
     int vec8;                  // rows of data start on 32-byte boundaries: one full sector per load
     int qbatch;                // queries of one partition a CTA takes together (1..kMaxQBatch)
+    int dense_cap;             // capacity of the dense pass's selection buffers: power of two >= kpart + blockDim/4
     FastDiv divT;
 };
 
-constexpr int kMaxQBatch = 4;                  // queries whose exhaustive distance phases share row loads
+constexpr int kMaxQBatch = 8;                  // queries whose exhaustive distance phases share row loads
 constexpr int kPromoPoints = 5;                // points a thread carries through the promotion phase
 constexpr int kDistChunk = 16;                 // floats of a row staged per step of the distance phase
 constexpr int kDistStride = kDistChunk + 4;    // padded row stride of the staging tile (floats)
@@ -621,7 +622,7 @@ traverse_kernel(const TraverseParams prm) {
       // 256-bit row loads, shared-memory buffers and room for Q selection buffer pairs)
       if (BATCH && ndense > 0) {
         if (prm.phase_cycles && tid == 0) t_last = clock64();
-        const size_t tk_bytes = TraverseLayout<ValT>::align16((size_t)prm.topk_cap * 8) * 2;
+        const size_t tk_bytes = (size_t)prm.dense_cap * 16;                      // two halves of u64[dense_cap]
         float *dq = reinterpret_cast<float *>(big + (size_t)Q * tk_bytes);       // Q query vectors
         for (int t = 0; t < ndense; ++t) {
             const float *src = prm.query + (size_t)(prm.q0 + s_dense[t]) * dim;
@@ -663,14 +664,18 @@ traverse_kernel(const TraverseParams prm) {
                 }
             }
             DCI_PHASE_MARK(5)
+            // the keys of a round are offered a quarter of the CTA at a time, so that a selection
+            // buffer only needs room for blockDim/4 appends
+            const int quarter = blockDim.x >> 2;
 #pragma unroll
             for (int t = 0; t < kMaxQBatch; ++t) {
                 if (t < ndense) {
                     uint64_t *bufs = reinterpret_cast<uint64_t *>(big + (size_t)t * tk_bytes);
-                    CtaTopK topk = topk_slot_open(&s_slot[t], bufs, s_sel, s_res, prm.topk_cap, prm.kpart);
+                    CtaTopK topk = topk_slot_open(&s_slot[t], bufs, s_sel, s_res, prm.dense_cap, prm.kpart);
                     const uint64_t key = live ? (((uint64_t)__float_as_uint(__fsqrt_rn(sq[t])) << 32) | (uint32_t)(lo + r))
                                               : kEmptySlot;
-                    topk.offer(key);
+                    for (int part = 0; part < 4; ++part)
+                        topk.offer_from((tid / quarter) == part ? key : kEmptySlot, quarter);
                     topk_slot_close(&s_slot[t], topk, bufs);
                 }
             }
@@ -678,7 +683,7 @@ traverse_kernel(const TraverseParams prm) {
         }
         for (int t = 0; t < ndense; ++t) {
             uint64_t *bufs = reinterpret_cast<uint64_t *>(big + (size_t)t * tk_bytes);
-            CtaTopK topk = topk_slot_open(&s_slot[t], bufs, s_sel, s_res, prm.topk_cap, prm.kpart);
+            CtaTopK topk = topk_slot_open(&s_slot[t], bufs, s_sel, s_res, prm.dense_cap, prm.kpart);
             topk.finish();
             uint64_t *out = prm.part_topk + ((size_t)s_dense[t] * prm.num_parts + b) * prm.kpart;
             const uint64_t *res = topk.result();

@@ -136,7 +136,8 @@ int dci_b200_get_work_stats(dci_b200_t *h, long long *h_out, long long capacity_
  * bucket counts, [2] window ranking inside buckets (or the radix-sort fallback),
  * [3] promotion iterations, [4] stop rule + candidate list (+ the counters
  * above), [5] distances, [6] top-k, [8] bucket scan, [9] bucket placement,
- * [10] counter reset; [15] = number of work items.  Synchronous. */
+ * [10] counter reset; [11] queries per CTA pass of the last launch (a host
+ * value); [15] = number of work items.  Synchronous. */
 int dci_b200_get_phase_cycles(dci_b200_t *h, long long *h_out);
 
 /* Number of kernels this library launched on behalf of this handle so far. */

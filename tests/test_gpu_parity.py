@@ -167,6 +167,21 @@ def test_large_k_uses_global_selection_buffers():
     _assert_same(ids, dists, oi, od, gs, os_, "large-k")
 
 
+@pytest.mark.parametrize("n,dim,L,S,P,nq,k", [(6000, 64, 2, 4, 2, 11, 10), (4000, 960, 3, 12, 2, 6, 10),
+                                              (5000, 24, 2, 3, 2, 19, 100), (30000, 40, 2, 10, 3, 5, 10)])
+def test_exhaustive_partitions_take_the_query_group_path(n, dim, L, S, P, nq, k):
+    """A quota no partition can meet makes every work item exhaustive; the library then answers
+    queries in groups whose distance pass loads each row once for the group.  Results must not change."""
+    rng = np.random.default_rng(n + dim)
+    c = dict(data=cases.latent_linear(rng, n, 8, dim, 0.01), query=cases.latent_linear(rng, nq, 8, dim, 0.01),
+             L=L, S=S, P=P, T=10, k=k, outer=5000, max_cand=1000000, proj=cases.unit_rows(rng, L * S, dim))
+    g, _, ids, dists, oi, od, gs, os_ = _run_both(c)
+    _assert_same(ids, dists, oi, od, gs, os_, "query-groups")
+    g.enable_work_stats(False, phases=True)
+    g.query(torch.from_numpy(c["query"]).cuda(), c["k"], c["outer"], max_num_candidates=c["max_cand"])
+    assert g.get_phase_cycles()["queries_per_pass"] > 1
+
+
 def test_query_host_buffers_match_device_buffers():
     c = cases.example_config(n=1000, nq=40)
     g = _dci(c)
