@@ -37,8 +37,10 @@ def _nvcc(kernel_src, util_src, include_dir, out):
     subprocess.run(cmd, check=True)
 
 
-def build_reference(ref_root="/root/reference", force=False):
-    """Returns the list of libraries built, or [] when the reference checkout is absent."""
+def build_reference(ref_root=None, force=False):
+    """Returns the list of libraries built, or [] when the reference checkout is absent.
+    ref_root defaults to $DCI_REFERENCE_ROOT, else the build machine's mount point."""
+    ref_root = ref_root or os.environ.get("DCI_REFERENCE_ROOT", "/root/reference")
     ksrc = os.path.join(ref_root, "src", "dci_cuda_kernel.cu")
     usrc = os.path.join(ref_root, "src", "util_kernel.cu")
     inc = os.path.join(ref_root, "include")
