@@ -312,7 +312,7 @@ def bench_ours(args):
                     "launch_ms": tr_ms, "project_ms": statistics.mean(pj), "merge_ms": statistics.mean(mg),
                     "entries_per_query": entries / nq, "candidates_per_query": cands / nq,
                     "phase_cycles_per_work_item": {k: v / max(phases["work_items"], 1) for k, v in phases.items()
-                                                   if k not in ("work_items", "queries_per_pass")},
+                                                   if k not in ("work_items", "queries_per_pass", "projection_tma")},
                     "queries_per_pass": phases["queries_per_pass"]}
         nrec = min(1000, nq)
         rec = recall_at_k(ids[:nrec] if world == 1 else ids[:nrec], data, query[:nrec], cfg["k"]) if world == 1 else None
@@ -422,7 +422,7 @@ def main():
     ap.add_argument("--queries", type=int, default=0, help="override the workload's number of queries")
     ap.add_argument("--ref-queries", type=int, default=256, help="cap on the reference arm's queries per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--projection", default="exact", choices=["exact", "tf32x3"],
+    ap.add_argument("--projection", default="exact", choices=["exact", "tf32x3", "tf32x3_plain"],
                     help="exact fp32 projection (default) or the tcgen05 3xTF32 kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)

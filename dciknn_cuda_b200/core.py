@@ -273,11 +273,13 @@ class DCI(object):
         out = {n: int(buf[i]) for i, n in enumerate(names) if n}
         out["work_items"] = int(buf[15])
         out["queries_per_pass"] = int(buf[11])
+        out["projection_tma"] = int(buf[13])
         return out
 
     def set_projection(self, mode):
-        """'exact' (default; fixed fp32 summation order) or 'tf32x3' (tcgen05 tensor cores)."""
-        rc = _capi.lib().dci_b200_set_projection(self._live(), {"exact": 0, "tf32x3": 1}[mode])
+        """'exact' (default; fixed fp32 summation order), 'tf32x3' (tcgen05 tensor cores, TMA-fed
+        when the shapes allow) or 'tf32x3_plain' (tensor cores, plain loads)."""
+        rc = _capi.lib().dci_b200_set_projection(self._live(), {"exact": 0, "tf32x3": 1, "tf32x3_plain": 2}[mode])
         if rc == _capi.ERR_STATE:
             raise RuntimeError(_capi.lib().dci_b200_last_error().decode())
         _capi.check(rc)

@@ -4,6 +4,7 @@
 // dci_init/dci_add/dci_query/dci_clear/dci_reset/dci_free
 // (src/dci_cuda_kernel.cu:93-110, 149-187, 777-899) and the Torch shim
 // (src/dci_cuda.cpp:54-173).
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdarg.h>
 #include <stdint.h>
@@ -67,6 +68,39 @@ struct DeviceGuard {
 
 int next_pow2(int x) { int p = 1; while (p < x) p <<= 1; return p; }
 
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// Tensor map over a row-major fp32 matrix [rows][dim] with boxes of [box_rows][32 columns] and the
+// 128-byte swizzle; out-of-range elements read as zero.
+bool make_tensor_map_2d(CUtensorMap *map, const float *ptr, long long rows, int dim, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn || dim % 4 != 0 || ((uintptr_t)ptr & 15) != 0 || box_rows < 1 || box_rows > 256 || rows < 1) return false;
+    const cuuint64_t dims[2] = {(cuuint64_t)dim, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)dim * sizeof(float)};
+    const cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1u, 1u};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)ptr, dims, strides, box, estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 }  // namespace
 
 struct dci_b200 {
@@ -79,6 +113,7 @@ struct dci_b200 {
     int stats_on = 0, stats_nq = 0, phases_valid = 0;
     int timing_on = 0;
     int last_qbatch = 1;                 // queries per CTA pass of the last traversal launch
+    int last_projection_tma = 0;
     int projection_mode = 0;             // 0: exact fp32 FMA order, 1: tensor cores, 3xTF32
     Buf errflag;
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
@@ -101,13 +136,24 @@ int launch_directions(dci_b200 *h, unsigned long long seed, cudaStream_t st) {
 int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cudaStream_t st) {
     if (n <= 0) return 0;
     const int I = h->L * h->S;
-    if (h->projection_mode == 1) {
+    if (h->projection_mode != 0) {
         DCI_CUDA(h->errflag.ensure(sizeof(int)));
         DCI_CUDA(cudaMemsetAsync(h->errflag.p, 0, sizeof(int), st));
         const unsigned tgrid = (unsigned)((n + dci::kTcPoints - 1) / dci::kTcPoints);
+        CUtensorMap map_x, map_p;
+        const bool tma = h->projection_mode == 1 && make_tensor_map_2d(&map_x, d_x, n, h->dim, dci::kTcPoints) &&
+                         make_tensor_map_2d(&map_p, h->d_proj, I, h->dim, dci::kTcDirs);
+        if (tma)
+            DCI_CUDA(cudaFuncSetAttribute(dci::project_tf32x3_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          (int)dci::kTcTmaSmem));
+        h->last_projection_tma = tma ? 1 : 0;
         for (int i0 = 0; i0 < I; i0 += dci::kTcDirs) {
-            dci::project_tf32x3_kernel<<<tgrid, dci::kTcPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, i0, d_out,
-                                                                       (int *)h->errflag.p);
+            if (tma)
+                dci::project_tf32x3_tma_kernel<<<tgrid, dci::kTcPoints, dci::kTcTmaSmem, st>>>(
+                    map_x, map_p, n, h->dim, I, i0, d_out, (int *)h->errflag.p);
+            else
+                dci::project_tf32x3_kernel<<<tgrid, dci::kTcPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, i0, d_out,
+                                                                           (int *)h->errflag.p);
             h->launches++;
             DCI_CUDA(cudaGetLastError());
         }
@@ -545,6 +591,7 @@ int dci_b200_get_phase_cycles(dci_b200_t *h, long long *h_out) {
     DCI_CUDA(cudaDeviceSynchronize());
     DCI_CUDA(cudaMemcpy(h_out, h->phases.p, sizeof(long long) * 16, cudaMemcpyDeviceToHost));
     h_out[11] = h->last_qbatch;
+    h_out[13] = h->last_projection_tma;
     return 0;
 }
 
@@ -552,7 +599,8 @@ long long dci_b200_launch_count(dci_b200_t *h) { return h ? h->launches : 0; }
 
 int dci_b200_set_projection(dci_b200_t *h, int mode) {
     if (int rc = check_handle(h)) return rc;
-    if (mode != 0 && mode != 1) return fail(DCI_B200_ERR_ARG, "projection mode must be 0 (exact) or 1 (tensor cores, 3xTF32)");
+    if (mode < 0 || mode > 2)
+        return fail(DCI_B200_ERR_ARG, "projection mode must be 0 (exact), 1 (tensor cores, TMA-fed) or 2 (tensor cores, plain loads)");
     if (h->num_points > 0) return fail(DCI_B200_ERR_STATE, "the projection mode cannot change while the index holds points; clear first");
     h->projection_mode = mode;
     return 0;

@@ -20,6 +20,8 @@
 // coalesced rows of `out`.  Every wait is bounded; on a time-out the kernel
 // raises *error, skips its stores, frees its tensor memory and returns.
 #pragma once
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace dci {
@@ -189,6 +191,182 @@ project_tf32x3_kernel(const float *__restrict__ x, long long n, int dim, const f
 #pragma unroll
             for (int c = 0; c < kTcDirs; ++c)
                 if (i0 + c < num_indices) out[(size_t)(i0 + c) * n + p] = __uint_as_float(r[c]);
+        }
+    } else if (tid == 0) {
+        atomicExch(error, 1);
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"((uint32_t)kTcDirs));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// The same contraction fed by TMA.  Per 32-coordinate slice one thread asks the
+// TMA unit for the [128 points x 32] tile of x and the [32 directions x 32] tile
+// of proj (128-byte swizzle; directions beyond L*S read as zero) into the next
+// stage of a 2-stage ring while the CTA works on the current one: all threads
+// split the landed tiles in place into the tf32 "hi" part and a separate "lo"
+// tile (an elementwise pass, so the swizzle needs no decoding), then one thread
+// issues the 4 x 3 MMAs (K-major, SWIZZLE_128B descriptors, K advanced by 32
+// bytes inside the swizzle atom) and commits them to the stage's "empty"
+// barrier, which the producer waits on before refilling it.
+// Dynamic shared memory: 2 stages x (A raw/hi 16 KB + A lo 16 KB + B raw/hi 4 KB + B lo 4 KB)
+// + 1 KB alignment slack.  Requires dim % 4 == 0 and 16-byte aligned x and proj.
+constexpr int kTcStages = 2;
+constexpr size_t kTcStageBytes = 2 * (kTcPoints * 128) + 2 * (kTcDirs * 128);
+constexpr size_t kTcTmaSmem = kTcStages * kTcStageBytes + 1024;
+
+// K-major, 128-byte swizzle: leading offset 1 (unused), stride (8 rows) 1024 bytes, version 1, layout type 2.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024u >> 4) << 32) |
+           (1ull << 46) | (2ull << 61);
+}
+
+__device__ __forceinline__ uint32_t mbar_wait(uint32_t bar, uint32_t parity) {
+    uint32_t done = 0;
+    for (uint32_t spin = 0; spin < kTcWaitLimit && !done; ++spin) {
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.b32 %0, 1, 0, p;\n\t"
+            "}\n"
+            : "=r"(done)
+            : "r"(bar), "r"(parity)
+            : "memory");
+    }
+    return done;
+}
+
+__global__ void __launch_bounds__(kTcPoints)
+project_tf32x3_tma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_p,
+                          long long n, int dim, int num_indices, int i0, float *__restrict__ out, int *error) {
+    extern __shared__ __align__(16) unsigned char tc_smem[];
+    __shared__ __align__(8) unsigned long long full_bar[kTcStages], empty_bar[kTcStages];
+    __shared__ uint32_t tmem_slot;
+
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const long long p0 = (long long)blockIdx.x * kTcPoints;
+    const uint32_t s0 = smem_u32(tc_smem);
+    unsigned char *base = tc_smem + (((s0 + 1023u) & ~1023u) - s0);
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"((uint32_t)kTcDirs));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    if (tid == 0) {
+        for (int s_ = 0; s_ < kTcStages; ++s_) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&full_bar[s_])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&empty_bar[s_])));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = tmem_slot;
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kTcDirs >> 3) << 17) |
+                           ((uint32_t)(kTcPoints >> 4) << 24);
+    const int nchunks = (dim + kTcK - 1) / kTcK;
+
+    auto request = [&](int c) {          // thread 0: TMA loads of slice c into stage c % 2
+        const int st = c % kTcStages;
+        unsigned char *sb = base + (size_t)st * kTcStageBytes;
+        const uint32_t bar = smem_u32(&full_bar[st]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                     "r"((uint32_t)(kTcPoints * 128 + kTcDirs * 128))
+                     : "memory");
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+                "r"(smem_u32(sb)), "l"(&map_x), "r"(c * kTcK), "r"((int)p0), "r"(bar)
+            : "memory");
+        asm volatile(
+            "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+                "r"(smem_u32(sb + 2 * kTcPoints * 128)), "l"(&map_p), "r"(c * kTcK), "r"(i0), "r"(bar)
+            : "memory");
+    };
+
+    int failed = 0;
+    uint32_t accumulate = 0;
+    if (tid == 0) request(0);
+    for (int c = 0; c < nchunks && !failed; ++c) {
+        const int st = c % kTcStages;
+        const uint32_t use = (uint32_t)(c / kTcStages);          // how often this stage was used before
+        unsigned char *sb = base + (size_t)st * kTcStageBytes;
+        // prefetch the next slice into the other stage once its previous MMAs have drained
+        if (tid == 0 && c + 1 < nchunks) {
+            const int nst = (c + 1) % kTcStages;
+            const uint32_t nuse = (uint32_t)((c + 1) / kTcStages);
+            uint32_t ok = 1;
+            if (nuse > 0) ok = mbar_wait(smem_u32(&empty_bar[nst]), (nuse - 1) & 1u);
+            if (ok) request(c + 1); else failed = 1;
+        }
+        if (!mbar_wait(smem_u32(&full_bar[st]), use & 1u)) failed = 1;
+        // split in place: hi stays where the tile landed, lo goes to the tile next to it
+        if (!failed) {
+            float4 *a_hi = reinterpret_cast<float4 *>(sb), *a_lo = reinterpret_cast<float4 *>(sb + kTcPoints * 128);
+            for (int f = tid; f < kTcPoints * 8; f += kTcPoints) {
+                const float4 v = a_hi[f];
+                float4 h, l;
+                split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+                a_hi[f] = h; a_lo[f] = l;
+            }
+            float4 *b_hi = reinterpret_cast<float4 *>(sb + 2 * kTcPoints * 128);
+            float4 *b_lo = reinterpret_cast<float4 *>(sb + 2 * kTcPoints * 128 + kTcDirs * 128);
+            for (int f = tid; f < kTcDirs * 8; f += kTcPoints) {
+                const float4 v = b_hi[f];
+                float4 h, l;
+                split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+                b_hi[f] = h; b_lo[f] = l;
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        failed = __syncthreads_or(failed);
+        if (failed) break;
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t ah = smem_u32(sb), al = ah + kTcPoints * 128, bh = ah + 2 * kTcPoints * 128, bl = bh + kTcDirs * 128;
+#pragma unroll
+            for (int kk = 0; kk < kTcK / 8; ++kk) {
+                const uint32_t step = kk * 32;              // 8 coordinates = 32 bytes inside the 128-byte atom
+                umma_tf32(tmem_d, umma_desc_sw128(al + step), umma_desc_sw128(bh + step), idesc, accumulate);
+                accumulate = 1;
+                umma_tf32(tmem_d, umma_desc_sw128(ah + step), umma_desc_sw128(bl + step), idesc, 1u);
+                umma_tf32(tmem_d, umma_desc_sw128(ah + step), umma_desc_sw128(bh + step), idesc, 1u);
+            }
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                             smem_u32(&empty_bar[st]))
+                         : "memory");
+        }
+    }
+    // the last slice's MMAs must have finished before the accumulator is read
+    if (!failed) {
+        const int lc = nchunks - 1;
+        if (!mbar_wait(smem_u32(&empty_bar[lc % kTcStages]), (uint32_t)(lc / kTcStages) & 1u)) failed = 1;
+    }
+    failed = __syncthreads_or(failed);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (!failed) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_d + ((uint32_t)(warp * 32) << 16);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        const long long p = p0 + tid;
+        if (p < n) {
+#pragma unroll
+            for (int cidx = 0; cidx < kTcDirs; ++cidx)
+                if (i0 + cidx < num_indices) out[(size_t)(i0 + cidx) * n + p] = __uint_as_float(r[cidx]);
         }
     } else if (tid == 0) {
         atomicExch(error, 1);

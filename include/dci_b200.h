@@ -136,8 +136,9 @@ int dci_b200_get_work_stats(dci_b200_t *h, long long *h_out, long long capacity_
  * bucket counts, [2] window ranking inside buckets (or the radix-sort fallback),
  * [3] promotion iterations, [4] stop rule + candidate list (+ the counters
  * above), [5] distances, [6] top-k, [8] bucket scan, [9] bucket placement,
- * [10] counter reset; [11] queries per CTA pass of the last launch (a host
- * value); [15] = number of work items.  Synchronous. */
+ * [10] counter reset; [11] queries per CTA pass of the last launch, [13] whether
+ * the last projection used the TMA-fed kernel (host values); [15] = number of
+ * work items.  Synchronous. */
 int dci_b200_get_phase_cycles(dci_b200_t *h, long long *h_out);
 
 /* Number of kernels this library launched on behalf of this handle so far. */
@@ -147,9 +148,11 @@ long long dci_b200_launch_count(dci_b200_t *h);
  * cublasSgemm calls of src/util_kernel.cu:45-80).  0 (default): exact fp32, one
  * fused multiply-add per term in ascending coordinate order -- the path every
  * parity test pins.  1: 5th-generation tensor cores (tcgen05.mma, fp32 operands
- * split into two tf32 terms, "3xTF32"); keys then differ from mode 0 by about
+ * split into two tf32 terms, "3xTF32"), operand tiles fetched by TMA when dim is
+ * a multiple of 4 and the pointers are 16-byte aligned; 2: the same without TMA
+ * (plain loads).  Keys of modes 1 and 2 differ from mode 0 by about
  * 1e-6 * |x|, which can move a point across a window boundary, so results are
- * not guaranteed identical to mode 0.  Mode 1 synchronises the stream after
+ * not guaranteed identical to mode 0.  Modes 1 and 2 synchronise the stream after
  * each projection to check its bounded waits.  Rejected while the index holds
  * points (data and queries must be projected the same way). */
 int dci_b200_set_projection(dci_b200_t *h, int mode);

@@ -12,14 +12,15 @@ from tests import cases
 pytestmark = pytest.mark.gpu
 
 
+@pytest.mark.parametrize("mode", ["tf32x3", "tf32x3_plain"])
 @pytest.mark.parametrize("n,dim,L,S", [(1000, 128, 2, 10), (777, 100, 2, 7), (300, 37, 3, 12), (5000, 960, 3, 12), (129, 8, 1, 1)])
-def test_tensor_core_keys_match_exact_keys(n, dim, L, S):
+def test_tensor_core_keys_match_exact_keys(n, dim, L, S, mode):
     from dciknn_cuda_b200 import DCI
     rng = np.random.default_rng(n + dim)
     x = rng.standard_normal((n, dim)).astype(np.float32)
     proj = cases.unit_rows(rng, L * S, dim)
     g = DCI(dim, L, S, proj=torch.from_numpy(proj))
-    g.set_projection("tf32x3")
+    g.set_projection(mode)
     got = g.project(torch.from_numpy(x).cuda()).cpu().numpy()
     want = oracle.project(proj, x)
     scale = np.linalg.norm(x, axis=1)[None, :]
