@@ -30,6 +30,7 @@ SYMBOLS = [
     ("dci_b200_reset", C.c_int, [_vp, C.c_ulonglong]),
     ("dci_b200_num_points", C.c_int, [_vp]),
     ("dci_b200_get_index", C.c_int, [_vp, _vp, _vp]),
+    ("dci_b200_set_index", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]),
     ("dci_b200_project", C.c_int, [_vp, _vp, C.c_int, _vp, _vp]),
     ("dci_b200_enable_work_stats", C.c_int, [_vp, C.c_int]),
     ("dci_b200_get_work_stats", C.c_int, [_vp, _vp, C.c_longlong]),

@@ -242,6 +242,43 @@ class DCI(object):
         _capi.check(_capi.lib().dci_b200_get_index(self._live(), C.c_void_p(keys.data_ptr()), C.c_void_p(ids.data_ptr())))
         return keys, ids
 
+    def set_index(self, data, keys, ids):
+        """Installs a sorted index built elsewhere (see get_index) for the CUDA tensor `data`."""
+        if self.num_points > 0:
+            raise RuntimeError("DCI class does not support insertion of more than one tensor. Must combine all tensors into one tensor before inserting")
+        self._check_data(data)
+        I = self._num_comp_indices * self._num_simp_indices
+        keys = torch.as_tensor(keys, dtype=torch.float32).cpu().contiguous()
+        ids = torch.as_tensor(ids, dtype=torch.int32).cpu().contiguous()
+        if tuple(keys.shape) != (I, data.shape[0]) or tuple(ids.shape) != (I, data.shape[0]):
+            raise ValueError("keys and ids must have shape [num_comp_indices * num_simp_indices, num_points]")
+        with torch.cuda.device(self._device):
+            _capi.check(_capi.lib().dci_b200_set_index(
+                self._live(), C.c_void_p(data.data_ptr()), data.shape[0], self._block_size, self._thread_size,
+                C.c_void_p(keys.data_ptr()), C.c_void_p(ids.data_ptr()), _stream_ptr(self._device)))
+        self.num_points = data.shape[0]
+        self._array = data
+
+    def save(self, path):
+        """Writes directions and sorted index to `path` (numpy .npz).  The data tensor is not saved."""
+        import numpy as np
+        keys, ids = self.get_index()
+        np.savez(path, proj=self.get_proj().numpy(), keys=keys.numpy(), ids=ids.numpy(),
+                 meta=np.array([self._dim, self._num_comp_indices, self._num_simp_indices, self._block_size,
+                                self._thread_size, self.num_points], np.int64))
+
+    @classmethod
+    def load(cls, path, data, device=0):
+        """Rebuilds an instance from save()'s file and the CUDA tensor the index was built on."""
+        import numpy as np
+        z = np.load(path)
+        dim, L, S, bs, ts, n = [int(v) for v in z["meta"]]
+        if data.shape[0] != n:
+            raise ValueError("the saved index holds %d points, the tensor %d" % (n, data.shape[0]))
+        g = cls(dim, L, S, bs, ts, device, proj=torch.from_numpy(z["proj"]))
+        g.set_index(data, z["keys"], z["ids"])
+        return g
+
     def project(self, x):
         """[L*S, n] projected keys of the rows of x (exact fp32 path)."""
         self._check_data(x)

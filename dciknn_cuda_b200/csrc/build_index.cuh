@@ -73,4 +73,31 @@ build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_in
     }
 }
 
+// Rebuilds the derived arrays (inverse positions and stride-T keys) from a sorted index that was
+// produced elsewhere (a saved index, or the reference's own `indices` array, include/dci.h:44).
+// One CTA per (simple index, partition) segment, looping.
+template <typename PosT>
+__global__ void derive_index_kernel(const float *__restrict__ skeys, const int *__restrict__ sids, int N,
+                                    int num_indices, int ppb, int num_parts, int T, PosT *__restrict__ spos,
+                                    float *__restrict__ skeysT, int *bad) {
+    const long long nseg = (long long)num_indices * num_parts;
+    for (long long seg = blockIdx.x; seg < nseg; seg += gridDim.x) {
+        const int i = (int)(seg / num_parts), b = (int)(seg % num_parts);
+        const long long lo = (long long)b * ppb;
+        const int n = (int)min((long long)ppb, (long long)N - lo);
+        const size_t row = (size_t)i * N + lo;
+        const int qn = n / T, rem = n % T;
+        for (int x = threadIdx.x; x < n; x += blockDim.x) {
+            const long long p = (long long)sids[row + x] - lo;
+            if (p < 0 || p >= n || (x > 0 && skeys[row + x] < skeys[row + x - 1])) {
+                atomicExch(bad, 1);        // id outside its partition or keys not ascending
+                continue;
+            }
+            spos[row + p] = (PosT)x;
+            const int r = x % T, j = x / T;
+            skeysT[row + r * qn + min(r, rem) + j] = skeys[row + x];
+        }
+    }
+}
+
 }  // namespace dci

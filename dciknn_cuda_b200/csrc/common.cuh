@@ -261,6 +261,7 @@ __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, i
         const int b = bucket_of(k, scale, last);
         const uint32_t lo = cnt[b], hi = cnt[b + 1];
         uint32_t r = lo;
+        if (hi - lo > 1)                                 // alone in its bucket: the rank is the bucket start
         for (uint32_t j0 = lo; j0 < hi; j0 += 4) {      // four bucket mates at a time: independent loads
             uint32_t other[4], kj[4];
 #pragma unroll
@@ -292,13 +293,14 @@ __device__ __forceinline__ void cta_select2(Get get, int cnt, int k1, int k2, in
         for (int i = tid; i < 512; i += blockDim.x) sel[i >> 8][i & 255] = 0u;
         __syncthreads();
         const uint32_t p0 = res[0], p1 = res[1];
+        const bool both = k1 != k2;                       // equal ranks: one histogram serves both
         for (int j = tid; j < cnt; j += blockDim.x) {
             const uint32_t v = get(j), hi = (shift + 8 >= 32) ? 0u : (v >> (shift + 8)), d = (v >> shift) & 255u;
             if (hi == p0) atomicAdd(&sel[0][d], 1u);
-            if (hi == p1) atomicAdd(&sel[1][d], 1u);
+            if (both && hi == p1) atomicAdd(&sel[1][d], 1u);
         }
         __syncthreads();
-        if (tid < 64) {           // warp 0 resolves the first rank, warp 1 the second
+        if (tid < (both ? 64 : 32)) {   // warp 0 resolves the first rank, warp 1 the second
             const int which = tid >> 5;
             const uint32_t want = res[2 + which];
             uint32_t c[8], sum = 0;
@@ -323,7 +325,7 @@ __device__ __forceinline__ void cta_select2(Get get, int cnt, int k1, int k2, in
         __syncthreads();
     }
     out[0] = res[0];
-    out[1] = res[1];
+    out[1] = k1 != k2 ? res[1] : res[0];
     __syncthreads();
 }
 

@@ -397,6 +397,56 @@ int dci_b200_add(dci_b200_t *h, const float *d_data, int num_points, int block_s
     return rc;
 }
 
+int dci_b200_set_index(dci_b200_t *h, const float *d_data, int num_points, int block_size, int thread_size,
+                       const float *h_keys, const int *h_ids, void *stream) {
+    if (int rc = check_handle(h)) return rc;
+    if (h->num_points > 0)
+        return fail(DCI_B200_ERR_STATE, "the index already holds %d points (clear first)", h->num_points);
+    if (!d_data || !h_keys || !h_ids) return fail(DCI_B200_ERR_ARG, "null pointer passed to set_index");
+    if (num_points <= 0 || block_size <= 0 || thread_size <= 0 || thread_size > 65536)
+        return fail(DCI_B200_ERR_ARG, "num_points, block_size and thread_size must be positive");
+    DeviceGuard g(h->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int I = h->L * h->S;
+    const int ppb = (num_points + block_size - 1) / block_size;
+    const int num_parts = (num_points + ppb - 1) / ppb;
+    {
+        int tshift = 0;
+        while ((1 << tshift) < thread_size) ++tshift;
+        const unsigned long long wcap = (unsigned long long)h->S * ((ppb + thread_size - 1) / thread_size + 2);
+        if ((wcap << tshift) >= 0xFFFFFFFFull ||
+            !dci::FastDiv::exact_for((uint32_t)thread_size, (uint64_t)ppb + 2ull * thread_size))
+            return fail(DCI_B200_ERR_UNSUPPORTED, "partition of %d points is too large for thread_size %d", ppb, thread_size);
+    }
+    const size_t n_entries = (size_t)I * num_points;
+    DCI_CUDA(h->keys.ensure(n_entries * sizeof(float)));
+    DCI_CUDA(h->ids.ensure(n_entries * sizeof(int)));
+    DCI_CUDA(h->keysT.ensure(n_entries * sizeof(float)));
+    DCI_CUDA(h->pos.ensure(n_entries * (ppb <= 65535 ? sizeof(uint16_t) : sizeof(uint32_t))));
+    DCI_CUDA(h->errflag.ensure(sizeof(int)));
+    DCI_CUDA(cudaMemsetAsync(h->errflag.p, 0, sizeof(int), st));
+    DCI_CUDA(cudaMemcpyAsync(h->keys.p, h_keys, n_entries * sizeof(float), cudaMemcpyHostToDevice, st));
+    DCI_CUDA(cudaMemcpyAsync(h->ids.p, h_ids, n_entries * sizeof(int), cudaMemcpyHostToDevice, st));
+    const unsigned grid = (unsigned)std::min<long long>((long long)I * num_parts, (long long)h->sm_count * 8);
+    if (ppb <= 65535)
+        dci::derive_index_kernel<uint16_t><<<grid, 256, 0, st>>>((const float *)h->keys.p, (const int *)h->ids.p, num_points,
+                                                                  I, ppb, num_parts, thread_size, (uint16_t *)h->pos.p,
+                                                                  (float *)h->keysT.p, (int *)h->errflag.p);
+    else
+        dci::derive_index_kernel<uint32_t><<<grid, 256, 0, st>>>((const float *)h->keys.p, (const int *)h->ids.p, num_points,
+                                                                  I, ppb, num_parts, thread_size, (uint32_t *)h->pos.p,
+                                                                  (float *)h->keysT.p, (int *)h->errflag.p);
+    h->launches++;
+    DCI_CUDA(cudaGetLastError());
+    int flag = 0;
+    DCI_CUDA(cudaMemcpyAsync(&flag, h->errflag.p, sizeof(int), cudaMemcpyDeviceToHost, st));
+    DCI_CUDA(cudaStreamSynchronize(st));
+    if (flag) return fail(DCI_B200_ERR_ARG, "the index is not valid: a segment is not ascending or holds an id outside its partition");
+    h->num_points = num_points; h->P = block_size; h->T = thread_size; h->ppb = ppb; h->num_parts = num_parts;
+    h->d_data = d_data;
+    return 0;
+}
+
 int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
                    int num_outer_iterations, int max_num_candidates, int blind, int block_size,
                    int thread_size, int *d_ids, float *d_dists, void *stream) {

@@ -116,6 +116,16 @@ int dci_b200_num_points(dci_b200_t *h);
  * reference's `indices` array (include/dci.h:44).  For tests.  Synchronous. */
 int dci_b200_get_index(dci_b200_t *h, float *h_keys, int *h_ids);
 
+/* Installs an index that was built elsewhere -- one saved with get_index, or the
+ * reference's own sorted `indices` array -- instead of projecting and sorting:
+ * h_keys / h_ids are host arrays [L*S][num_points] in get_index's layout, built
+ * for the same directions, block_size and thread_size.  The derived arrays are
+ * rebuilt on the device; a segment that is not ascending, or an id outside its
+ * partition, is rejected with DCI_B200_ERR_ARG.  d_data is borrowed as in add.
+ * (The reference cannot save or load an index.)  Synchronous. */
+int dci_b200_set_index(dci_b200_t *h, const float *d_data, int num_points, int block_size, int thread_size,
+                       const float *h_keys, const int *h_ids, void *stream);
+
 /* Projects n rows of d_x on the handle's directions with the library's exact
  * fp32 path: d_out[i][p] = <proj[i], x[p]>, layout [L*S][n].  For tests. */
 int dci_b200_project(dci_b200_t *h, const float *d_x, int n, float *d_out, void *stream);
