@@ -385,7 +385,7 @@ struct CtaTopK {
     __device__ __forceinline__ void compact() {   // all threads; keeps the k smallest, sorted
         int c = *count;
         __syncthreads();
-        if (c > k) {
+        if (c > k && c > 128) {       // a short list is cheaper to sort outright
             uint32_t tau[2];
             const uint64_t *src = buf;
             cta_select2([src](int j) { return (uint32_t)(src[j] >> 32); }, c, k, k, 32, sel, res, tau);
