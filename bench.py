@@ -422,7 +422,7 @@ def main():
     ap.add_argument("--queries", type=int, default=0, help="override the workload's number of queries")
     ap.add_argument("--ref-queries", type=int, default=256, help="cap on the reference arm's queries per step")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--projection", default="exact", choices=["exact", "tf32x3", "tf32x3_plain"],
+    ap.add_argument("--projection", default="exact", choices=["exact", "tf32x3", "tf32x3_plain", "tf32x3_tile"],
                     help="exact fp32 projection (default) or the tcgen05 3xTF32 kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else max(args.warmup, 1)

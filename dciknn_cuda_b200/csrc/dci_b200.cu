@@ -141,14 +141,22 @@ int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cud
         DCI_CUDA(cudaMemsetAsync(h->errflag.p, 0, sizeof(int), st));
         const unsigned tgrid = (unsigned)((n + dci::kTcPoints - 1) / dci::kTcPoints);
         CUtensorMap map_x, map_p;
-        const bool tma = h->projection_mode == 1 && make_tensor_map_2d(&map_x, d_x, n, h->dim, dci::kTcPoints) &&
+        const bool tma = h->projection_mode != 2 && make_tensor_map_2d(&map_x, d_x, n, h->dim, dci::kTcPoints) &&
                          make_tensor_map_2d(&map_p, h->d_proj, I, h->dim, dci::kTcDirs);
-        if (tma)
+        const bool persistent = tma && h->projection_mode == 1;
+        if (persistent)
+            DCI_CUDA(cudaFuncSetAttribute(dci::project_tf32x3_persistent_kernel,
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dci::kPsSmem));
+        else if (tma)
             DCI_CUDA(cudaFuncSetAttribute(dci::project_tf32x3_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)dci::kTcTmaSmem));
         h->last_projection_tma = tma ? 1 : 0;
         for (int i0 = 0; i0 < I; i0 += dci::kTcDirs) {
-            if (tma)
+            if (persistent)
+                dci::project_tf32x3_persistent_kernel<<<std::min<unsigned>(tgrid, (unsigned)h->sm_count), dci::kPsThreads,
+                                                        dci::kPsSmem, st>>>(map_x, map_p, n, h->dim, I, i0, d_out,
+                                                                            (int *)h->errflag.p);
+            else if (tma)
                 dci::project_tf32x3_tma_kernel<<<tgrid, dci::kTcPoints, dci::kTcTmaSmem, st>>>(
                     map_x, map_p, n, h->dim, I, i0, d_out, (int *)h->errflag.p);
             else
@@ -649,8 +657,9 @@ long long dci_b200_launch_count(dci_b200_t *h) { return h ? h->launches : 0; }
 
 int dci_b200_set_projection(dci_b200_t *h, int mode) {
     if (int rc = check_handle(h)) return rc;
-    if (mode < 0 || mode > 2)
-        return fail(DCI_B200_ERR_ARG, "projection mode must be 0 (exact), 1 (tensor cores, TMA-fed) or 2 (tensor cores, plain loads)");
+    if (mode < 0 || mode > 3)
+        return fail(DCI_B200_ERR_ARG, "projection mode must be 0 (exact), 1 (tensor cores, persistent TMA pipeline), "
+                                      "2 (tensor cores, plain loads) or 3 (tensor cores, one TMA-fed tile per CTA)");
     if (h->num_points > 0) return fail(DCI_B200_ERR_STATE, "the projection mode cannot change while the index holds points; clear first");
     h->projection_mode = mode;
     return 0;

@@ -378,4 +378,179 @@ project_tf32x3_tma_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
     }
 }
 
+// ---------------------------------------------------------------------------
+// Persistent, warp-specialised form of the TMA-fed kernel.  One CTA per SM loops
+// over 128-point tiles.  Roles:
+//   warp 0, one lane  : producer -- TMA loads of the next 32-coordinate slice (points + directions)
+//                       into a 4-stage ring, as soon as the stage's previous MMAs have drained;
+//   warps 2..5        : converters -- split the landed slice into hi / lo tf32 tiles, then, once a
+//                       tile's last MMAs are committed, read its accumulator from tensor memory and
+//                       store the keys (the accumulator is double buffered, so the MMAs of the next
+//                       tile run during these stores);
+//   warp 1, one lane  : MMA issuer -- 4 x 3 tcgen05.mma per converted slice, committed to the
+//                       stage's "empty" barrier, and after a tile's last slice to "accumulator full".
+// All hand-offs are mbarriers; every wait is bounded and a time-out makes all roles leave.
+constexpr int kPsStages = 4;
+constexpr int kPsThreads = 192;
+constexpr size_t kPsSmem = kPsStages * kTcStageBytes + 1024;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__global__ void __launch_bounds__(kPsThreads, 1)
+project_tf32x3_persistent_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_p,
+                                 long long n, int dim, int num_indices, int i0, float *__restrict__ out, int *error) {
+    extern __shared__ __align__(16) unsigned char tc_smem[];
+    __shared__ __align__(8) unsigned long long full_bar[kPsStages], conv_bar[kPsStages], empty_bar[kPsStages];
+    __shared__ __align__(8) unsigned long long acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_slot;
+    __shared__ volatile int abort_flag;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t s0 = smem_u32(tc_smem);
+    unsigned char *base = tc_smem + (((s0 + 1023u) & ~1023u) - s0);
+
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
+                     "r"((uint32_t)(2 * kTcDirs)));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    if (tid == 0) {
+        abort_flag = 0;
+        for (int s_ = 0; s_ < kPsStages; ++s_) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&full_bar[s_])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(smem_u32(&conv_bar[s_])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&empty_bar[s_])));
+        }
+        for (int a = 0; a < 2; ++a) {
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&acc_full[a])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(smem_u32(&acc_empty[a])));
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_slot;
+    const int nchunks = (dim + kTcK - 1) / kTcK;
+    const long long ntiles = (n + kTcPoints - 1) / kTcPoints;
+    const uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kTcDirs >> 3) << 17) |
+                           ((uint32_t)(kTcPoints >> 4) << 24);
+
+    if (warp == 0 && lane == 0) {
+        // ---- producer
+        uint32_t q = 0;                                   // slices requested so far
+        for (long long tile = blockIdx.x; tile < ntiles && !abort_flag; tile += gridDim.x) {
+            for (int c = 0; c < nchunks; ++c, ++q) {
+                const int st = (int)(q % kPsStages);
+                const uint32_t use = q / kPsStages;
+                if (use > 0 && !mbar_wait(smem_u32(&empty_bar[st]), (use - 1) & 1u)) { abort_flag = 1; break; }
+                unsigned char *sb = base + (size_t)st * kTcStageBytes;
+                const uint32_t bar = smem_u32(&full_bar[st]);
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar),
+                             "r"((uint32_t)(kTcPoints * 128 + kTcDirs * 128))
+                             : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+                        "r"(smem_u32(sb)), "l"(&map_x), "r"(c * kTcK), "r"((int)(tile * kTcPoints)), "r"(bar)
+                    : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+                        "r"(smem_u32(sb + 2 * kTcPoints * 128)), "l"(&map_p), "r"(c * kTcK), "r"(i0), "r"(bar)
+                    : "memory");
+            }
+        }
+    } else if (warp == 1 && lane == 0) {
+        // ---- MMA issuer
+        uint32_t q = 0, t = 0;
+        for (long long tile = blockIdx.x; tile < ntiles && !abort_flag; tile += gridDim.x, ++t) {
+            const int a = (int)(t & 1u);
+            const uint32_t ause = t >> 1;                 // earlier tiles on this accumulator
+            if (ause > 0 && !mbar_wait(smem_u32(&acc_empty[a]), (ause - 1) & 1u)) { abort_flag = 1; break; }
+            const uint32_t tmem_d = tmem_base + (uint32_t)(a * kTcDirs);
+            for (int c = 0; c < nchunks; ++c, ++q) {
+                const int st = (int)(q % kPsStages);
+                if (!mbar_wait(smem_u32(&conv_bar[st]), (q / kPsStages) & 1u)) { abort_flag = 1; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t ah = smem_u32(base + (size_t)st * kTcStageBytes), al = ah + kTcPoints * 128,
+                               bh = ah + 2 * kTcPoints * 128, bl = bh + kTcDirs * 128;
+#pragma unroll
+                for (int kk = 0; kk < kTcK / 8; ++kk) {
+                    const uint32_t step = kk * 32;
+                    umma_tf32(tmem_d, umma_desc_sw128(al + step), umma_desc_sw128(bh + step), idesc, (c | kk) ? 1u : 0u);
+                    umma_tf32(tmem_d, umma_desc_sw128(ah + step), umma_desc_sw128(bl + step), idesc, 1u);
+                    umma_tf32(tmem_d, umma_desc_sw128(ah + step), umma_desc_sw128(bh + step), idesc, 1u);
+                }
+                asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                                 smem_u32(&empty_bar[st]))
+                             : "memory");
+            }
+            if (abort_flag) break;
+            asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                             smem_u32(&acc_full[a]))
+                         : "memory");
+        }
+    } else if (warp >= 2) {
+        // ---- converters and epilogue: 128 threads
+        const int ct = tid - 64;
+        uint32_t q = 0, t = 0;
+        for (long long tile = blockIdx.x; tile < ntiles && !abort_flag; tile += gridDim.x, ++t) {
+            for (int c = 0; c < nchunks; ++c, ++q) {
+                const int st = (int)(q % kPsStages);
+                if (!mbar_wait(smem_u32(&full_bar[st]), (q / kPsStages) & 1u)) { abort_flag = 1; break; }
+                unsigned char *sb = base + (size_t)st * kTcStageBytes;
+                float4 *a_hi = reinterpret_cast<float4 *>(sb), *a_lo = reinterpret_cast<float4 *>(sb + kTcPoints * 128);
+                for (int f = ct; f < kTcPoints * 8; f += 128) {
+                    const float4 v = a_hi[f];
+                    float4 h, l;
+                    split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+                    a_hi[f] = h; a_lo[f] = l;
+                }
+                float4 *b_hi = reinterpret_cast<float4 *>(sb + 2 * kTcPoints * 128);
+                float4 *b_lo = reinterpret_cast<float4 *>(sb + 2 * kTcPoints * 128 + kTcDirs * 128);
+                for (int f = ct; f < kTcDirs * 8; f += 128) {
+                    const float4 v = b_hi[f];
+                    float4 h, l;
+                    split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
+                    b_hi[f] = h; b_lo[f] = l;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                mbar_arrive(smem_u32(&conv_bar[st]));
+            }
+            if (abort_flag) break;
+            // epilogue of this tile
+            const int a = (int)(t & 1u);
+            if (!mbar_wait(smem_u32(&acc_full[a]), (t >> 1) & 1u)) { abort_flag = 1; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t r[32];
+            const uint32_t taddr = tmem_base + (uint32_t)(a * kTcDirs) + ((uint32_t)((warp & 3) * 32) << 16);
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                : "r"(taddr));
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(smem_u32(&acc_empty[a]));
+            const long long p = tile * kTcPoints + (warp & 3) * 32 + lane;     // TMEM lane = point of the tile
+            if (p < n) {
+#pragma unroll
+                for (int cidx = 0; cidx < kTcDirs; ++cidx)
+                    if (i0 + cidx < num_indices) out[(size_t)(i0 + cidx) * n + p] = __uint_as_float(r[cidx]);
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (tid == 0 && abort_flag) atomicExch(error, 1);
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * kTcDirs)));
+    }
+}
+
 }  // namespace dci

@@ -158,11 +158,12 @@ long long dci_b200_launch_count(dci_b200_t *h);
  * cublasSgemm calls of src/util_kernel.cu:45-80).  0 (default): exact fp32, one
  * fused multiply-add per term in ascending coordinate order -- the path every
  * parity test pins.  1: 5th-generation tensor cores (tcgen05.mma, fp32 operands
- * split into two tf32 terms, "3xTF32"), operand tiles fetched by TMA when dim is
- * a multiple of 4 and the pointers are 16-byte aligned; 2: the same without TMA
- * (plain loads).  Keys of modes 1 and 2 differ from mode 0 by about
+ * split into two tf32 terms, "3xTF32") in persistent, warp-specialised CTAs fed
+ * by TMA (when dim is a multiple of 4 and the pointers are 16-byte aligned;
+ * otherwise as mode 2); 2: the same MMAs with plain loads; 3: one TMA-fed tile
+ * per CTA.  Keys of modes 1-3 differ from mode 0 by about
  * 1e-6 * |x|, which can move a point across a window boundary, so results are
- * not guaranteed identical to mode 0.  Modes 1 and 2 synchronise the stream after
+ * not guaranteed identical to mode 0.  Modes 1-3 synchronise the stream after
  * each projection to check its bounded waits.  Rejected while the index holds
  * points (data and queries must be projected the same way). */
 int dci_b200_set_projection(dci_b200_t *h, int mode);

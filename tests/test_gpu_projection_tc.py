@@ -12,8 +12,8 @@ from tests import cases
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("mode", ["tf32x3", "tf32x3_plain"])
-@pytest.mark.parametrize("n,dim,L,S", [(1000, 128, 2, 10), (777, 100, 2, 7), (300, 37, 3, 12), (5000, 960, 3, 12), (129, 8, 1, 1)])
+@pytest.mark.parametrize("mode", ["tf32x3", "tf32x3_plain", "tf32x3_tile"])
+@pytest.mark.parametrize("n,dim,L,S", [(1000, 128, 2, 10), (777, 100, 2, 7), (300, 37, 3, 12), (5000, 960, 3, 12), (129, 8, 1, 1), (40000, 64, 2, 10)])
 def test_tensor_core_keys_match_exact_keys(n, dim, L, S, mode):
     from dciknn_cuda_b200 import DCI
     rng = np.random.default_rng(n + dim)
