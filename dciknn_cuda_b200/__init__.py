@@ -3,5 +3,6 @@
 Reference surface: dciknn_cuda/__init__.py:22 exports DCI and MDCI.
 """
 from .core import DCI, MDCI, merge_shards, shard_bounds
+from . import tuning
 
-__all__ = ["DCI", "MDCI", "merge_shards", "shard_bounds"]
+__all__ = ["DCI", "MDCI", "merge_shards", "shard_bounds", "tuning"]

@@ -61,6 +61,7 @@ class DCI(object):
         self._thread_size = ts
         self._device = _device_index(device)
         self._array = None
+        self._store = None
         self.num_points = 0
         self._handle = C.c_void_p()
         lib = _capi.lib()
@@ -138,6 +139,34 @@ class DCI(object):
                                                 self._block_size, self._thread_size, _stream_ptr(self._device)))
         self.num_points = data.shape[0]
         self._array = data          # the index borrows the tensor's memory
+        self._store = None
+
+    def append(self, data):
+        """Adds more rows to a non-empty index (the reference has no such call: its add refuses a
+        second tensor, dciknn_cuda/core.py:70-71).  The result equals clear() followed by add() of the
+        concatenation of everything added so far, but only the new rows are projected.  The index
+        keeps its own copy of the rows from the first append on (capacity grows geometrically), since
+        the rows must be contiguous."""
+        if self.num_points == 0:
+            raise RuntimeError("append needs a non-empty index; use add first")
+        self._check_data(data)
+        if data.device.index != self._device:
+            raise ValueError("data must be on the index's device")
+        n_old, n_add = self.num_points, data.shape[0]
+        if n_add == 0:
+            return
+        n_new = n_old + n_add
+        with torch.cuda.device(self._device):
+            store = self._store
+            if store is None or store.shape[0] < n_new:
+                store = torch.empty((max(n_new, n_old + n_old // 2), self._dim), dtype=torch.float32, device=data.device)
+                store[:n_old].copy_(self._array[:n_old])
+            store[n_old:n_new].copy_(data)
+            _capi.check(_capi.lib().dci_b200_append(self._live(), C.c_void_p(store.data_ptr()), n_new,
+                                                   _stream_ptr(self._device)))
+        self._store = store
+        self._array = store[:n_new]
+        self.num_points = n_new
 
     def query(self, query, num_neighbours=-1, num_outer_iterations=5000, blind=False, *,
               max_num_candidates=None, return_int_ids=False):
@@ -214,11 +243,13 @@ class DCI(object):
         _capi.check(_capi.lib().dci_b200_clear(self._live()))
         self.num_points = 0
         self._array = None
+        self._store = None
 
     def reset(self, *, seed=None):
         _capi.check(_capi.lib().dci_b200_reset(self._live(), _default_seed() if seed is None else int(seed)))
         self.num_points = 0
         self._array = None
+        self._store = None
 
     def free(self):
         if self._handle:
@@ -226,6 +257,7 @@ class DCI(object):
             self._handle = C.c_void_p()
         self.num_points = 0
         self._array = None
+        self._store = None
 
     def __del__(self):
         try:

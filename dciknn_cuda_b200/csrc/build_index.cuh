@@ -100,4 +100,15 @@ __global__ void derive_index_kernel(const float *__restrict__ skeys, const int *
     }
 }
 
+// Inverse of the build's sort, for appending rows: writes the key of point ids[i][x] back to
+// out[i][ids[i][x]], `out` having rows of `out_stride` floats.
+__global__ void unsort_keys_kernel(const float *__restrict__ skeys, const int *__restrict__ sids, int N,
+                                   int num_indices, float *__restrict__ out, int out_stride) {
+    const long long total = (long long)num_indices * N;
+    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
+        const long long i = e / N;
+        out[i * out_stride + sids[e]] = skeys[e];
+    }
+}
+
 }  // namespace dci

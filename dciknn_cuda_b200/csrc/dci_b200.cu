@@ -367,6 +367,26 @@ int dci_b200_set_proj(dci_b200_t *h, const float *h_in) {
     return 0;
 }
 
+// Limits shared by add and append: the encoded promotion (rank << tshift | lane) must fit 32 bits.
+static int check_partition_limits(dci_b200 *h, int ppb, int thread_size) {
+    int tshift = 0;
+    while ((1 << tshift) < thread_size) ++tshift;
+    const unsigned long long wcap = (unsigned long long)h->S * ((ppb + thread_size - 1) / thread_size + 2);
+    if ((wcap << tshift) >= 0xFFFFFFFFull ||
+        !dci::FastDiv::exact_for((uint32_t)thread_size, (uint64_t)ppb + 2ull * thread_size))
+        return fail(DCI_B200_ERR_UNSUPPORTED, "partition of %d points with %d simple indices and thread_size %d is too large",
+                    ppb, h->S, thread_size);
+    return 0;
+}
+
+static int ensure_index_buffers(dci_b200 *h, size_t n_entries, int ppb) {
+    DCI_CUDA(h->keys.ensure(n_entries * sizeof(float)));
+    DCI_CUDA(h->ids.ensure(n_entries * sizeof(int)));
+    DCI_CUDA(h->keysT.ensure(n_entries * sizeof(float)));
+    DCI_CUDA(h->pos.ensure(n_entries * (ppb <= 65535 ? sizeof(uint16_t) : sizeof(uint32_t))));
+    return 0;
+}
+
 int dci_b200_add(dci_b200_t *h, const float *d_data, int num_points, int block_size, int thread_size, void *stream) {
     if (int rc = check_handle(h)) return rc;
     if (h->num_points > 0)
@@ -381,26 +401,55 @@ int dci_b200_add(dci_b200_t *h, const float *d_data, int num_points, int block_s
     const int I = h->L * h->S;
     const int ppb = (num_points + block_size - 1) / block_size;
     const int num_parts = (num_points + ppb - 1) / ppb;
-    {   // encoded promotion (rank << tshift | lane) must fit 32 bits
-        int tshift = 0;
-        while ((1 << tshift) < thread_size) ++tshift;
-        const unsigned long long wcap = (unsigned long long)h->S * ((ppb + thread_size - 1) / thread_size + 2);
-        if ((wcap << tshift) >= 0xFFFFFFFFull ||
-            !dci::FastDiv::exact_for((uint32_t)thread_size, (uint64_t)ppb + 2ull * thread_size))
-            return fail(DCI_B200_ERR_UNSUPPORTED, "partition of %d points with %d simple indices and thread_size %d is too large",
-                        ppb, h->S, thread_size);
-    }
+    if (int rc = check_partition_limits(h, ppb, thread_size)) return rc;
     const size_t n_entries = (size_t)I * num_points;
-    DCI_CUDA(h->keys.ensure(n_entries * sizeof(float)));
-    DCI_CUDA(h->ids.ensure(n_entries * sizeof(int)));
-    DCI_CUDA(h->keysT.ensure(n_entries * sizeof(float)));
-    DCI_CUDA(h->pos.ensure(n_entries * (ppb <= 65535 ? sizeof(uint16_t) : sizeof(uint32_t))));
+    if (int rc = ensure_index_buffers(h, n_entries, ppb)) return rc;
     DCI_CUDA(h->tmp_keys.ensure(n_entries * sizeof(float)));
     h->num_points = num_points; h->P = block_size; h->T = thread_size; h->ppb = ppb; h->num_parts = num_parts;
     h->d_data = d_data;
     int rc = launch_project(h, d_data, num_points, (float *)h->tmp_keys.p, st);
     if (!rc) rc = (ppb <= 65535) ? launch_build<uint16_t>(h, (const float *)h->tmp_keys.p, st)
                                  : launch_build<uint32_t>(h, (const float *)h->tmp_keys.p, st);
+    if (rc) { h->num_points = 0; h->d_data = nullptr; }
+    return rc;
+}
+
+int dci_b200_append(dci_b200_t *h, const float *d_all_data, int num_points_total, void *stream) {
+    if (int rc = check_handle(h)) return rc;
+    if (h->num_points <= 0) return fail(DCI_B200_ERR_STATE, "append needs an index that already holds points (add first)");
+    if (!d_all_data) return fail(DCI_B200_ERR_ARG, "d_all_data is null");
+    if (num_points_total <= h->num_points)
+        return fail(DCI_B200_ERR_ARG, "num_points_total (%d) must exceed the %d points already indexed", num_points_total,
+                    h->num_points);
+    DeviceGuard g(h->device);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int I = h->L * h->S, n_old = h->num_points, n_new = num_points_total, n_add = n_new - n_old;
+    const int ppb = (n_new + h->P - 1) / h->P;
+    const int num_parts = (n_new + ppb - 1) / ppb;
+    if (int rc = check_partition_limits(h, ppb, h->T)) return rc;
+    // 1. the old rows' keys, back in id order, at the new row stride
+    DCI_CUDA(h->tmp_keys.ensure((size_t)I * n_new * sizeof(float)));
+    {
+        const long long total = (long long)I * n_old;
+        const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)h->sm_count * 8);
+        dci::unsort_keys_kernel<<<grid, 256, 0, st>>>((const float *)h->keys.p, (const int *)h->ids.p, n_old, I,
+                                                      (float *)h->tmp_keys.p, n_new);
+        h->launches++;
+        DCI_CUDA(cudaGetLastError());
+    }
+    // 2. keys of the new rows only (staged in the stride-T buffer, which step 3 rewrites anyway)
+    DCI_CUDA(cudaStreamSynchronize(st));       // growing a buffer frees it: nothing may still read it
+    DCI_CUDA(h->keysT.ensure((size_t)I * n_new * sizeof(float)));
+    if (int rc = launch_project(h, d_all_data + (size_t)n_old * h->dim, n_add, (float *)h->keysT.p, st)) return rc;
+    DCI_CUDA(cudaMemcpy2DAsync((float *)h->tmp_keys.p + n_old, (size_t)n_new * sizeof(float), h->keysT.p,
+                               (size_t)n_add * sizeof(float), (size_t)n_add * sizeof(float), (size_t)I,
+                               cudaMemcpyDeviceToDevice, st));
+    DCI_CUDA(cudaStreamSynchronize(st));
+    // 3. every segment again, for the partition bounds of the new point count
+    if (int rc = ensure_index_buffers(h, (size_t)I * n_new, ppb)) { h->num_points = 0; h->d_data = nullptr; return rc; }
+    h->num_points = n_new; h->ppb = ppb; h->num_parts = num_parts; h->d_data = d_all_data;
+    int rc = (ppb <= 65535) ? launch_build<uint16_t>(h, (const float *)h->tmp_keys.p, st)
+                            : launch_build<uint32_t>(h, (const float *)h->tmp_keys.p, st);
     if (rc) { h->num_points = 0; h->d_data = nullptr; }
     return rc;
 }

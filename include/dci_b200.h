@@ -77,6 +77,18 @@ int dci_b200_set_proj(dci_b200_t *h, const float *h_in);
 int dci_b200_add(dci_b200_t *h, const float *d_data, int num_points, int block_size,
                  int thread_size, void *stream);
 
+/* No counterpart in the reference, whose dci_add refuses a second array
+ * (src/dci_cuda_kernel.cu:157, dciknn_cuda/core.py:70-71): grows an index that
+ * already holds N0 points to num_points_total > N0 points.  d_all_data is
+ * [num_points_total][dim]; its first N0 rows must be the rows already indexed,
+ * unchanged (the caller appends in place or copies them).  Only the new rows
+ * are projected; the old rows' keys are recovered from the sorted index; every
+ * segment is then sorted again for the partition bounds of the new count
+ * (ppb = ceil(num_points_total / P), with the P and T of the first add).  The
+ * result is the index dci_b200_add would build from d_all_data, bit for bit.
+ * The index borrows d_all_data from then on.  Synchronises the stream. */
+int dci_b200_append(dci_b200_t *h, const float *d_all_data, int num_points_total, void *stream);
+
 /* Replaces dci_query (include/dci.h:71-75, src/dci_cuda_kernel.cu:777-875) and
  * _dci_query: for each of the num_queries rows of d_query returns the
  * num_neighbours candidates nearest in Euclidean distance among the points the
