@@ -735,7 +735,6 @@ int dci_b200_merge_shards(const int *d_ids_in, const float *d_dists_in, int num_
         return fail(DCI_B200_ERR_ARG, "null pointer passed to merge_shards");
     if (num_shards <= 0 || num_shards > 64 || num_queries < 0 || k <= 0)
         return fail(DCI_B200_ERR_ARG, "merge_shards needs 1..64 shards, num_queries >= 0 and k > 0");
-    if (k > dci::kMaxTopK) return fail(DCI_B200_ERR_UNSUPPORTED, "k above %d is not supported yet", dci::kMaxTopK);
     if (num_queries == 0) return 0;
     for (int s = 0; s < num_shards; ++s)
         if (id_offsets[s] < 0 || id_offsets[s] > 0x7FFFFFFFll)
@@ -747,8 +746,12 @@ int dci_b200_merge_shards(const int *d_ids_in, const float *d_dists_in, int num_
     memset(&off, 0, sizeof(off));
     for (int s = 0; s < num_shards; ++s) off.v[s] = id_offsets[s];
     const int threads = 256, cap = next_pow2(k + threads);
-    dci::merge_shards_kernel<<<num_queries, threads, (size_t)cap * 16, st>>>(
-        d_ids_in, d_dists_in, num_shards, num_queries, k, cap, off, d_ids_out, d_dists_out);
+    if (k > dci::kMaxTopK)      // lists too long for the selection buffers: merge by rank (sorted input)
+        dci::merge_shards_sorted_kernel<<<num_queries, threads, 0, st>>>(d_ids_in, d_dists_in, num_shards, num_queries, k,
+                                                                        off, d_ids_out, d_dists_out);
+    else
+        dci::merge_shards_kernel<<<num_queries, threads, (size_t)cap * 16, st>>>(
+            d_ids_in, d_dists_in, num_shards, num_queries, k, cap, off, d_ids_out, d_dists_out);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(DCI_B200_ERR_CUDA, "merge_shards launch: %s", cudaGetErrorString(e));
     return 0;

@@ -781,4 +781,59 @@ __global__ void merge_shards_kernel(const int *__restrict__ ids_in, const float 
     }
 }
 
+// The same merge for k above the selection buffers' limit.  Needs every shard's list sorted
+// ascending by (distance, id) with its empty slots (id < 0) last, which is what a query returns:
+// the place of an entry in the merged list is then the number of entries of all lists that
+// precede it, found with one binary search per shard.  One CTA per query.
+__global__ void merge_shards_sorted_kernel(const int *__restrict__ ids_in, const float *__restrict__ dists_in,
+                                           int num_shards, int nq, int k, const ShardOffsets offsets,
+                                           long long *__restrict__ out_ids, float *__restrict__ out_dists) {
+    __shared__ int s_valid[64];
+    __shared__ int s_total;
+    const int q = blockIdx.x;
+    auto key_at = [&](int s, int r) {
+        const size_t src = ((size_t)s * nq + q) * k + r;
+        return ((uint64_t)__float_as_uint(dists_in[src]) << 32) | (uint32_t)((long long)ids_in[src] + offsets.v[s]);
+    };
+    for (int s = threadIdx.x; s < num_shards; s += blockDim.x) {   // entries before the first empty slot
+        int lo = 0, hi = k;
+        while (lo < hi) {
+            const int mid = (lo + hi) >> 1;
+            if (ids_in[((size_t)s * nq + q) * k + mid] >= 0) lo = mid + 1; else hi = mid;
+        }
+        s_valid[s] = lo;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int s = 0; s < num_shards; ++s) t += s_valid[s];
+        s_total = t;
+    }
+    __syncthreads();
+    const long long total = (long long)num_shards * k;
+    for (long long j = threadIdx.x; j < total; j += blockDim.x) {
+        const int s = (int)(j / k), r = (int)(j % k);
+        if (r >= s_valid[s]) continue;
+        const uint64_t key = key_at(s, r);
+        int place = r;
+        for (int s2 = 0; s2 < num_shards && place < k; ++s2) {
+            if (s2 == s) continue;
+            int lo = 0, hi = s_valid[s2];
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (key_at(s2, mid) < key) lo = mid + 1; else hi = mid;
+            }
+            place += lo;
+        }
+        if (place < k) {
+            out_ids[(size_t)q * k + place] = (long long)(uint32_t)key;
+            out_dists[(size_t)q * k + place] = __uint_as_float((uint32_t)(key >> 32));
+        }
+    }
+    for (int j = s_total + threadIdx.x; j < k; j += blockDim.x) {
+        out_ids[(size_t)q * k + j] = -1;
+        out_dists[(size_t)q * k + j] = __int_as_float(0x7F800000);
+    }
+}
+
 }  // namespace dci

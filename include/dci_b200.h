@@ -196,6 +196,9 @@ int dci_b200_get_timing(dci_b200_t *h, float *h_ms);
  * reference adds data_per_device * s, core.py:149); ties go to the lower
  * global id, which for sorted shard lists equals the reference's stable sort
  * of the shard-ordered concatenation.  Negative ids (empty slots) stay -1.
+ * For k above 1024 every shard list must be sorted ascending by (distance,
+ * id) with its empty slots last, as dci_b200_query returns it; the merge then
+ * places each entry by binary searches instead of a selection.
  * d_ids_out: [num_queries][k] int64; d_dists_out: [num_queries][k] fp32. */
 int dci_b200_merge_shards(const int *d_ids_in, const float *d_dists_in, int num_shards,
                           int num_queries, int k, const long long *id_offsets,
