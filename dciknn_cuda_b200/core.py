@@ -179,13 +179,23 @@ class DCI(object):
         if num_neighbours < 0:
             num_neighbours = self.num_points
         self._ensure_positive_integer(num_neighbours)
-        if blind:
-            raise NotImplementedError("blind querying is not supported")
         if max_num_candidates is None:
             max_num_candidates = 10 * num_neighbours
         if self.num_points == 0:
             raise RuntimeError("the index is empty; add data first")
         nq = _query.shape[0]
+        if blind:
+            # Candidates in order of retrieval, no distances (reference dci_cuda_kernel.cu:398-399, :775-776);
+            # returns ([nq, width] ids, [nq, width] promotion iterations), -1 in unused slots.
+            width = _capi.lib().dci_b200_blind_width(int(num_outer_iterations), int(max_num_candidates))
+            with torch.cuda.device(self._device):
+                ids = torch.empty((nq, width), dtype=torch.int32, device=_query.device)
+                iters = torch.empty((nq, width), dtype=torch.int32, device=_query.device)
+                _capi.check(_capi.lib().dci_b200_query_blind(
+                    self._live(), C.c_void_p(_query.data_ptr()), nq, num_neighbours, int(num_outer_iterations),
+                    int(max_num_candidates), self._block_size, self._thread_size,
+                    C.c_void_p(ids.data_ptr()), C.c_void_p(iters.data_ptr()), _stream_ptr(self._device)))
+            return (ids, iters) if return_int_ids else (ids.to(torch.float32), iters)
         with torch.cuda.device(self._device):
             ids = torch.empty((nq, num_neighbours), dtype=torch.int32, device=_query.device)
             dists = torch.empty((nq, num_neighbours), dtype=torch.float32, device=_query.device)
@@ -461,7 +471,7 @@ class MDCI(object):
         if num_neighbours <= 0:
             raise RuntimeError('num_neighbours must be positive')
         if blind:
-            raise NotImplementedError("blind querying is not supported")
+            raise NotImplementedError("blind querying is per index: the retrieval orders of different shards cannot be merged")
         _query = query.unsqueeze(0) if len(query.shape) < 2 else query
         k = num_neighbours
         if self._pg is None:

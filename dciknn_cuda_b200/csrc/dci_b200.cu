@@ -255,7 +255,7 @@ int launch_traverse(dci_b200 *h, dci::TraverseParams prm, int nthreads, cudaStre
     // promotions, so a quota well above that (with an iteration cap beyond the last window) is never met
     prm.qbatch = 1;
     const bool likely_exhaustive = (long long)prm.max_cand * prm.T * 2 > 3ll * prm.ppb && prm.outer_s >= prm.wcap;
-    if (smem && prm.vec8 && !prm.topk_global && likely_exhaustive) {
+    if (smem && prm.vec8 && !prm.topk_global && !prm.blind && likely_exhaustive) {
         prm.dense_cap = next_pow2(prm.kpart + nthreads / 4);
         const size_t per_q = (size_t)prm.dense_cap * 16 + (size_t)prm.dim * 4 + 16;
         prm.qbatch = (int)std::max<size_t>(1, std::min<size_t>(dci::kMaxQBatch, lay.big_bytes / per_q));
@@ -504,15 +504,15 @@ int dci_b200_set_index(dci_b200_t *h, const float *d_data, int num_points, int b
     return 0;
 }
 
-int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
-                   int num_outer_iterations, int max_num_candidates, int blind, int block_size,
-                   int thread_size, int *d_ids, float *d_dists, void *stream) {
+// out_width: entries per query in the outputs (num_neighbours, or the candidate list length of a blind query)
+static int query_impl(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
+                      int num_outer_iterations, int max_num_candidates, int blind, int out_width, int block_size,
+                      int thread_size, int *d_ids, float *d_dists, void *stream) {
     if (int rc = check_handle(h)) return rc;
-    if (blind) return fail(DCI_B200_ERR_UNSUPPORTED, "blind querying is not supported");
     if (h->num_points <= 0) return fail(DCI_B200_ERR_STATE, "the index is empty; add data first");
     if (num_queries < 0) return fail(DCI_B200_ERR_ARG, "num_queries must not be negative");
     if (num_queries == 0) return 0;
-    if (!d_query || !d_ids || !d_dists) return fail(DCI_B200_ERR_ARG, "null query or output pointer");
+    if (!d_query || !d_ids || (!d_dists && !blind)) return fail(DCI_B200_ERR_ARG, "null query or output pointer");
     if (num_neighbours <= 0) return fail(DCI_B200_ERR_ARG, "num_neighbours must be positive, got %d", num_neighbours);
     if (num_neighbours > h->num_points)
         return fail(DCI_B200_ERR_ARG, "num_neighbours (%d) exceeds the number of indexed points (%d)", num_neighbours, h->num_points);
@@ -549,11 +549,14 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
     prm.vec4 = (h->dim % 4 == 0) && (((uintptr_t)h->d_data & 15) == 0) && (((uintptr_t)d_query & 15) == 0);
     prm.vec8 = (h->dim % 8 == 0) && (((uintptr_t)h->d_data & 31) == 0);
     const int nthreads = prm.wcap >= 4096 ? 1024 : (prm.wcap >= 1024 ? 512 : 256);
-    prm.kpart = std::min(num_neighbours, h->ppb);
+    prm.blind = blind ? 1 : 0;
+    prm.kpart = std::min(out_width, h->ppb);
     prm.topk_cap = next_pow2(prm.kpart + nthreads);
-    prm.topk_global = prm.topk_cap > 2048 ? 1 : 0;      // larger selection buffers do not fit shared memory
+    // larger selection buffers do not fit shared memory; a blind query reads the promotion records
+    // while it selects, and the shared buffers would overlay them
+    prm.topk_global = (prm.topk_cap > 2048 || blind) ? 1 : 0;
     const int merge_threads = 256;
-    const int merge_cap = next_pow2(num_neighbours + merge_threads);
+    const int merge_cap = next_pow2(out_width + merge_threads);
     const bool merge_global = merge_cap > 2048;
 
     if (h->stats_on & 2) {
@@ -589,8 +592,8 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
         if (timing) DCI_CUDA(cudaEventRecord(h->ev[3], st));
         dci::merge_partitions_kernel<<<std::min(prm.nq, merge_grid_cap), merge_threads,
                                        merge_global ? 0 : (size_t)merge_cap * 16, st>>>(
-            prm.part_topk, h->num_parts, prm.kpart, num_neighbours, merge_cap, q0, prm.nq,
-            merge_global ? (uint64_t *)h->merge_scratch.p : nullptr, d_ids, d_dists);
+            prm.part_topk, h->num_parts, prm.kpart, out_width, merge_cap, q0, prm.nq,
+            merge_global ? (uint64_t *)h->merge_scratch.p : nullptr, d_ids, d_dists, prm.blind);
         h->launches++;
         DCI_CUDA(cudaGetLastError());
         if (timing) {   // timing mode synchronises after every batch; it is off by default
@@ -604,6 +607,28 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
         }
     }
     return 0;
+}
+
+int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
+                   int num_outer_iterations, int max_num_candidates, int blind, int block_size,
+                   int thread_size, int *d_ids, float *d_dists, void *stream) {
+    if (blind)
+        return fail(DCI_B200_ERR_UNSUPPORTED, "blind querying returns lists of another length: use dci_b200_query_blind");
+    return query_impl(h, d_query, num_queries, num_neighbours, num_outer_iterations, max_num_candidates, 0,
+                      num_neighbours, block_size, thread_size, d_ids, d_dists, stream);
+}
+
+int dci_b200_blind_width(int num_outer_iterations, int max_num_candidates) {
+    return std::max(0, std::min(num_outer_iterations, max_num_candidates));
+}
+
+int dci_b200_query_blind(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
+                         int num_outer_iterations, int max_num_candidates, int block_size, int thread_size,
+                         int *d_ids, int *d_iterations, void *stream) {
+    const int width = dci_b200_blind_width(num_outer_iterations, max_num_candidates);
+    if (width <= 0) return fail(DCI_B200_ERR_ARG, "num_outer_iterations and max_num_candidates must be positive");
+    return query_impl(h, d_query, num_queries, num_neighbours, num_outer_iterations, max_num_candidates, 1, width,
+                      block_size, thread_size, d_ids, reinterpret_cast<float *>(d_iterations), stream);
 }
 
 int dci_b200_query_host(dci_b200_t *h, const float *h_query, int num_queries, int num_neighbours,
@@ -831,7 +856,7 @@ int query_noalloc_impl(dci_b200 *h, dci::TraverseParams prm, int nthreads, unsig
         h->launches++;
         DCI_CUDA(cudaGetLastError());
         dci::merge_partitions_kernel<<<prm.nq, merge_threads, (size_t)merge_cap * 16, st>>>(
-            prm.part_topk, prm.num_parts, prm.kpart, prm.knn, merge_cap, q0, prm.nq, nullptr, d_ids, d_dists);
+            prm.part_topk, prm.num_parts, prm.kpart, prm.knn, merge_cap, q0, prm.nq, nullptr, d_ids, d_dists, 0);
         h->launches++;
         DCI_CUDA(cudaGetLastError());
     }

@@ -66,6 +66,7 @@ struct TraverseParams {
     int vec8;                  // rows of data start on 32-byte boundaries: one full sector per load
     int qbatch;                // queries of one partition a CTA takes together (1..kMaxQBatch)
     int dense_cap;             // capacity of the dense pass's selection buffers: power of two >= kpart + blockDim/4
+    int blind;                 // 1: no distances; a promoted point's key is its promotion iteration (needs topk_global)
     FastDiv divT;
 };
 
@@ -590,7 +591,12 @@ traverse_kernel(const TraverseParams prm) {
         for (int base = 0; base < ncand; base += blockDim.x) {
             uint64_t key = kEmptySlot;
             const int j = base + tid;
-            if (prm.vec8) {
+            if (prm.blind) {             // blind querying (reference :398-399): order of retrieval, no row is read
+                if (j < ncand) {
+                    const uint32_t p = (uint32_t)list[j];
+                    key = ((uint64_t)(kenc[p] >> prm.tshift) << 32) | (uint32_t)(lo + p);
+                }
+            } else if (prm.vec8) {
                 if (j < ncand) {
                     const long long gid = lo + (long long)list[j];
                     const float d = dist_sequential_v8(prm.data + (size_t)gid * dim, qvec, dim);
@@ -700,9 +706,11 @@ traverse_kernel(const TraverseParams prm) {
 // get_top_candidates, src/dci_cuda_kernel.cu:691-701).  CTAs loop over queries.
 // The selection buffers are dynamic shared memory, or -- for large k -- the
 // CTA's slab of `gbufs` (2 * topk_cap entries each).
+// blind: the high word of a key is a promotion iteration; out_dists then receives int32 values
+// (-1 in empty slots) and may be null.
 __global__ void merge_partitions_kernel(const uint64_t *__restrict__ part_topk, int num_parts, int kpart,
                                         int knn, int topk_cap, int q0, int nq, uint64_t *gbufs,
-                                        int *__restrict__ out_ids, float *__restrict__ out_dists) {
+                                        int *__restrict__ out_ids, float *__restrict__ out_dists, int blind) {
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     __shared__ int s_count;
     __shared__ uint64_t s_thresh;
@@ -725,10 +733,10 @@ __global__ void merge_partitions_kernel(const uint64_t *__restrict__ part_topk, 
             const size_t o = (size_t)(q0 + ql) * knn + j;
             if (key == kEmptySlot) {
                 out_ids[o] = -1;
-                out_dists[o] = __int_as_float(0x7F800000);
+                if (out_dists) out_dists[o] = blind ? __int_as_float(-1) : __int_as_float(0x7F800000);
             } else {
                 out_ids[o] = (int)(uint32_t)key;
-                out_dists[o] = __uint_as_float((uint32_t)(key >> 32));
+                if (out_dists) out_dists[o] = __uint_as_float((uint32_t)(key >> 32));   // blind: the iteration as int32 bits
             }
         }
         __syncthreads();

@@ -107,6 +107,26 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
                    int num_outer_iterations, int max_num_candidates, int blind,
                    int block_size, int thread_size, int *d_ids, float *d_dists, void *stream);
 
+/* A working form of the reference's blind querying, which its comments specify
+ * (src/dci_cuda_kernel.cu:398-399, :775-776: no distance is computed, no
+ * indexed vector is read, the result is the candidates "in the order of
+ * retrieval", max_possible_num_candidates = min(max_num_candidates,
+ * num_outer_iterations) per query, :784-785) but whose code cannot run
+ * (unsynchronised candidate counter :498-505, host reads of device memory
+ * :770-772, output sized for k ids by src/dci_cuda.cpp:99-100).  The traversal
+ * and its stop rule are those of dci_b200_query with the same arguments.
+ * Partitions are traversed side by side, so "order of retrieval" is defined
+ * as ascending (iteration of the partition's loop at which the point was
+ * promoted, point id).  d_ids: [num_queries][width] int32 with width =
+ * dci_b200_blind_width(num_outer_iterations, max_num_candidates), -1 in unused
+ * slots; d_iterations: the same shape, the promotion iterations (-1 in unused
+ * slots), or NULL.  dci_b200_query itself refuses blind != 0 because its
+ * outputs have another length. */
+int dci_b200_blind_width(int num_outer_iterations, int max_num_candidates);
+int dci_b200_query_blind(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
+                         int num_outer_iterations, int max_num_candidates, int block_size,
+                         int thread_size, int *d_ids, int *d_iterations, void *stream);
+
 /* Same query with HOST buffers: copies the queries to the device, runs the
  * query and copies ids and distances back.  Synchronous. */
 int dci_b200_query_host(dci_b200_t *h, const float *h_query, int num_queries, int num_neighbours,

@@ -179,7 +179,7 @@ static void traverse_partition(const float *skeys, const int *sids, int N, int L
                                int knn, long long outer, int max_cand,
                                unsigned char *cand, int *counts /* [L][n] scratch */,
                                int *left, int *right, int *cur, float *prio,
-                               work_stats_t *st) {
+                               work_stats_t *st, long long *when /* optional [n]: iteration of promotion */) {
     int I = L * S;
     memset(cand, 0, (size_t)n);
     memset(counts, 0, sizeof(int) * (size_t)L * n);
@@ -223,6 +223,7 @@ static void traverse_partition(const float *skeys, const int *sids, int N, int L
                 st->entries++;
                 if (++counts[(long long)m * n + p] == S && !cand[p]) {
                     cand[p] = 1;
+                    if (when) when[p] = k;
                     st->candidates++;
                     if (t == 0) { c0++; }
                 }
@@ -304,7 +305,7 @@ int dci_oracle_query(const float *skeys, const int *sids, int N, int L, int S, i
                     memset(&st, 0, sizeof(st));
                     if (n > 0) {
                         traverse_partition(skeys, sids, N, L, S, lo, (int)n, T, qp, knn, outer,
-                                           max_cand, cand, counts, lr, lr + I, lr + 2 * I, prio, &st);
+                                           max_cand, cand, counts, lr, lr + I, lr + 2 * I, prio, &st, NULL);
                         for (int x = 0; x < n; ++x) {
                             if (!cand[x]) continue;
                             int p = (int)(lo + x);
@@ -333,6 +334,76 @@ int dci_oracle_query(const float *skeys, const int *sids, int N, int L, int S, i
             }
         }
         free(cand); free(counts); free(lr); free(prio); free(qp); free(list);
+    }
+    return err ? -2 : 0;
+}
+
+typedef struct { long long when; int id; } blind_t;
+
+static int blind_cmp(const void *a, const void *b) {
+    const blind_t *x = (const blind_t *)a, *y = (const blind_t *)b;
+    if (x->when != y->when) return x->when < y->when ? -1 : 1;
+    return (x->id > y->id) - (x->id < y->id);
+}
+
+/*
+ * Blind querying as the reference's comments specify it (dci_cuda_kernel.cu:398-399, :775-776):
+ * the same traversal with the same stop rule, no distance is computed and no indexed vector is
+ * read; the result is the promoted points "in the order of retrieval".  Partitions are traversed
+ * side by side (one CUDA block each, :843), so the order is defined here as ascending
+ * (iteration of the partition's loop at which the point was promoted, point id).  The reference's
+ * own blind path cannot be run (unsynchronised counter :498-505, host reads of device memory
+ * :770-772), so this restatement is the specification, not a transcription.
+ *   out_ids / out_when  [nq][width]; unused slots hold -1 / -1.
+ */
+int dci_oracle_query_blind(const float *skeys, const int *sids, int N, int L, int S, int P, int T,
+                           const float *qproj, int nq, int knn, long long outer, int max_cand,
+                           int width, int *out_ids, long long *out_when) {
+    if (!skeys || !sids || !qproj || !out_ids) return -1;
+    if (N <= 0 || L <= 0 || S <= 0 || P <= 0 || T <= 0 || nq < 0 || knn <= 0 || width <= 0) return -1;
+    int I = L * S;
+    int ppb = (N + P - 1) / P;
+    int err = 0;
+#pragma omp parallel
+    {
+        unsigned char *cand = (unsigned char *)malloc((size_t)ppb);
+        int *counts = (int *)malloc(sizeof(int) * (size_t)L * ppb);
+        int *lr = (int *)malloc(sizeof(int) * 3 * (size_t)I);
+        float *prio = (float *)malloc(sizeof(float) * (size_t)I);
+        float *qp = (float *)malloc(sizeof(float) * (size_t)I);
+        long long *when = (long long *)malloc(sizeof(long long) * (size_t)ppb);
+        blind_t *list = (blind_t *)malloc(sizeof(blind_t) * (size_t)N);
+        if (!cand || !counts || !lr || !prio || !qp || !when || !list) {
+#pragma omp atomic write
+            err = 1;
+        } else {
+#pragma omp for schedule(dynamic)
+            for (int q = 0; q < nq; ++q) {
+                for (int i = 0; i < I; ++i) qp[i] = qproj[(long long)i * nq + q];
+                int cnt = 0;
+                for (int b = 0; b < P; ++b) {
+                    long long lo = (long long)b * ppb;
+                    long long n = (long long)N - lo;
+                    if (n > ppb) n = ppb;
+                    if (n <= 0) continue;
+                    work_stats_t st;
+                    traverse_partition(skeys, sids, N, L, S, lo, (int)n, T, qp, knn, outer, max_cand,
+                                       cand, counts, lr, lr + I, lr + 2 * I, prio, &st, when);
+                    for (int x = 0; x < n; ++x) {
+                        if (!cand[x]) continue;
+                        list[cnt].id = (int)(lo + x);
+                        list[cnt].when = when[x];
+                        cnt++;
+                    }
+                }
+                qsort(list, (size_t)cnt, sizeof(blind_t), blind_cmp);
+                for (int j = 0; j < width; ++j) {
+                    out_ids[(long long)q * width + j] = j < cnt ? list[j].id : -1;
+                    if (out_when) out_when[(long long)q * width + j] = j < cnt ? list[j].when : -1;
+                }
+            }
+        }
+        free(cand); free(counts); free(lr); free(prio); free(qp); free(when); free(list);
     }
     return err ? -2 : 0;
 }

@@ -26,6 +26,8 @@ def lib():
         _lib.dci_oracle_query.argtypes = [fp, ip, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                           fp, C.c_int, fp, fp, C.c_int, C.c_int, ll, C.c_int,
                                           ip, fp, C.POINTER(ll), C.POINTER(C.c_ubyte)]
+        _lib.dci_oracle_query_blind.argtypes = [fp, ip, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                fp, C.c_int, C.c_int, ll, C.c_int, C.c_int, ip, C.POINTER(ll)]
         _lib.dci_oracle_bruteforce.argtypes = [fp, C.c_int, C.c_int, fp, C.c_int, C.c_int, ip, fp]
         _lib.dci_oracle_num_threads.restype = C.c_int
         _lib.dci_oracle_set_num_threads.argtypes = [C.c_int]
@@ -89,6 +91,21 @@ def query_index(skeys, sids, L, S, P, T, data, qproj, query, k, outer, max_cand,
     return tuple(out)
 
 
+def query_index_blind(skeys, sids, L, S, P, T, qproj, k, outer, max_cand, width):
+    """Blind traversal (no distances): ([nq, width] ids in retrieval order, [nq, width] iteration
+    of promotion); unused slots hold -1."""
+    skeys, qproj = _f32(skeys), _f32(qproj)
+    sids = np.ascontiguousarray(sids, dtype=np.int32)
+    N, nq = skeys.shape[1], qproj.shape[1]
+    ids = np.empty((nq, width), np.int32)
+    when = np.empty((nq, width), np.int64)
+    rc = lib().dci_oracle_query_blind(_p(skeys, C.c_float), _p(sids, C.c_int), N, L, S, P, T,
+                                      _p(qproj, C.c_float), nq, k, int(outer), int(max_cand), int(width),
+                                      _p(ids, C.c_int), _p(when, C.c_longlong))
+    assert rc == 0
+    return ids, when
+
+
 def bruteforce(data, query, k):
     data, query = _f32(data), _f32(query)
     ids = np.empty((query.shape[0], k), np.int32)
@@ -123,6 +140,16 @@ class OracleDCI:
         qproj = project(self.proj, query)
         return query_index(self.skeys, self.sids, self.L, self.S, self.P, self.T, self.data,
                            qproj, query, k, num_outer_iterations, mc, want_stats, want_mask)
+
+    def query_blind(self, query, num_neighbours=-1, num_outer_iterations=5000, max_num_candidates=None):
+        """Promoted point ids in retrieval order and their promotion iterations, each
+        [nq, min(max_num_candidates, num_outer_iterations)] (dci_cuda_kernel.cu:775-776, :784-785)."""
+        query = _f32(query).reshape(-1, self.dim)
+        k = self.num_points if num_neighbours < 0 else num_neighbours
+        mc = 10 * k if max_num_candidates is None else max_num_candidates
+        width = min(mc, num_outer_iterations)
+        return query_index_blind(self.skeys, self.sids, self.L, self.S, self.P, self.T,
+                                 project(self.proj, query), k, num_outer_iterations, mc, width)
 
 
 class OracleMDCI:

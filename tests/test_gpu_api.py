@@ -33,8 +33,8 @@ def test_argument_checks_follow_the_reference():
         g.query(good[:2], 0)
     with pytest.raises(ValueError):
         g.query(good[:2], 51)
-    with pytest.raises(NotImplementedError):
-        g.query(good[:2], 3, blind=True)
+    bi, bw = g.query(good[:2], 3, blind=True)      # candidates in retrieval order, width min(5000, 10 * 3)
+    assert bi.shape == bw.shape == (2, 30)
     ids, dists = g.query(good[:3])          # num_neighbours = -1 means all points (core.py:84-85)
     assert ids.shape == (3, 50) and bool((dists[:, 1:] >= dists[:, :-1]).all())
     assert torch.equal(ids[:, 0].long().cpu(), torch.arange(3))   # a point is its own nearest neighbour
