@@ -1,12 +1,15 @@
 // Index build: one stable radix sort per (simple index, partition) segment.
 // Replaces copy_to_indices + sort_indices (+ the recursive device quicksort)
 // of the reference (src/dci_cuda_kernel.cu:113-146, 190-247).  The result is
-// kept as flat arrays keys[L*S][N] / ids[L*S][N] (SoA) instead of the
-// reference's array of {key, id} structs (include/dci.h:27-30), plus the
-// inverse permutation pos[L*S][N]: pos[i][p] = position of point p inside its
-// partition's sorted segment of simple index i (16-bit when partitions hold
-// fewer than 65 536 points), which lets a query look a point's window up
-// directly instead of scattering over index entries.  A third copy of the keys,
+// kept as flat arrays keys / ids (SoA) instead of the reference's array of
+// {key, id} structs (include/dci.h:27-30), plus the inverse permutation pos:
+// the position of point p inside its partition's sorted segment of simple
+// index i (16-bit when partitions hold fewer than 65 536 points), which lets a
+// query look a point's window up directly instead of scattering over index
+// entries.  All four arrays are PARTITION-MAJOR: the I segments of a partition
+// lie next to each other (segment_start), so that a work item of the traversal
+// -- one query against one partition -- touches one contiguous range of each
+// array instead of I ranges that are N entries apart.  A third copy of the keys,
 // keysT, holds every segment "stride-T transposed": the key at sorted position
 // y = j*T + r sits at r*(n/T) + min(r, n%T) + j, so that the keys at positions
 // r, r+T, r+2T, ... -- the window starts of one query -- are contiguous.
@@ -54,9 +57,10 @@ build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_in
         const int i = (int)(seg / num_parts), b = (int)(seg % num_parts);
         const long long lo = (long long)b * ppb;
         const int n = (int)min((long long)ppb, (long long)N - lo);
-        const size_t row = (size_t)i * N + lo;
+        const size_t row = segment_start(lo, i, num_indices, n);
+        const size_t urow = (size_t)i * N + lo;               // the projection writes [I][N]
         for (int x = threadIdx.x; x < n; x += blockDim.x) {
-            kA[x] = float_to_ordered(keys_unsorted[row + x]);
+            kA[x] = float_to_ordered(keys_unsorted[urow + x]);
             vA[x] = (ValT)x;
         }
         __syncthreads();
@@ -73,41 +77,71 @@ build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_in
     }
 }
 
-// Rebuilds the derived arrays (inverse positions and stride-T keys) from a sorted index that was
-// produced elsewhere (a saved index, or the reference's own `indices` array, include/dci.h:44).
-// One CTA per (simple index, partition) segment, looping.
+// Installs a sorted index that was produced elsewhere (a saved index, or the reference's own
+// `indices` array, include/dci.h:44): in_keys / in_ids are [I][N] with every partition's segment
+// sorted; the kernel checks them and writes the partition-major keys, ids, inverse positions and
+// stride-T keys.  One CTA per (simple index, partition) segment, looping.
 template <typename PosT>
-__global__ void derive_index_kernel(const float *__restrict__ skeys, const int *__restrict__ sids, int N,
-                                    int num_indices, int ppb, int num_parts, int T, PosT *__restrict__ spos,
-                                    float *__restrict__ skeysT, int *bad) {
+__global__ void derive_index_kernel(const float *__restrict__ in_keys, const int *__restrict__ in_ids, int N,
+                                    int num_indices, int ppb, int num_parts, int T, float *__restrict__ skeys,
+                                    int *__restrict__ sids, PosT *__restrict__ spos, float *__restrict__ skeysT,
+                                    int *bad) {
     const long long nseg = (long long)num_indices * num_parts;
     for (long long seg = blockIdx.x; seg < nseg; seg += gridDim.x) {
         const int i = (int)(seg / num_parts), b = (int)(seg % num_parts);
         const long long lo = (long long)b * ppb;
         const int n = (int)min((long long)ppb, (long long)N - lo);
-        const size_t row = (size_t)i * N + lo;
+        const size_t row = segment_start(lo, i, num_indices, n);
+        const size_t urow = (size_t)i * N + lo;
         const int qn = n / T, rem = n % T;
         for (int x = threadIdx.x; x < n; x += blockDim.x) {
-            const long long p = (long long)sids[row + x] - lo;
-            if (p < 0 || p >= n || (x > 0 && skeys[row + x] < skeys[row + x - 1])) {
+            const long long p = (long long)in_ids[urow + x] - lo;
+            const float key = in_keys[urow + x];
+            if (p < 0 || p >= n || (x > 0 && key < in_keys[urow + x - 1])) {
                 atomicExch(bad, 1);        // id outside its partition or keys not ascending
                 continue;
             }
+            skeys[row + x] = key;
+            sids[row + x] = in_ids[urow + x];
             spos[row + p] = (PosT)x;
             const int r = x % T, j = x / T;
-            skeysT[row + r * qn + min(r, rem) + j] = skeys[row + x];
+            skeysT[row + r * qn + min(r, rem) + j] = key;
         }
     }
 }
 
-// Inverse of the build's sort, for appending rows: writes the key of point ids[i][x] back to
-// out[i][ids[i][x]], `out` having rows of `out_stride` floats.
+// Sorted index back to [I][N] arrays: out_keys / out_ids (either may be null) receive the sorted
+// segments in the layout callers see (dci_b200_get_index).
+__global__ void export_index_kernel(const float *__restrict__ skeys, const int *__restrict__ sids, int N,
+                                    int num_indices, int ppb, int num_parts, float *__restrict__ out_keys,
+                                    int *__restrict__ out_ids) {
+    const long long nseg = (long long)num_indices * num_parts;
+    for (long long seg = blockIdx.x; seg < nseg; seg += gridDim.x) {
+        const int i = (int)(seg / num_parts), b = (int)(seg % num_parts);
+        const long long lo = (long long)b * ppb;
+        const int n = (int)min((long long)ppb, (long long)N - lo);
+        const size_t row = segment_start(lo, i, num_indices, n);
+        const size_t urow = (size_t)i * N + lo;
+        for (int x = threadIdx.x; x < n; x += blockDim.x) {
+            if (out_keys) out_keys[urow + x] = skeys[row + x];
+            if (out_ids) out_ids[urow + x] = sids[row + x];
+        }
+    }
+}
+
+// Inverse of the build's sort, for appending rows: writes the key of every indexed point back to
+// out[i][id], `out` having rows of `out_stride` floats.
 __global__ void unsort_keys_kernel(const float *__restrict__ skeys, const int *__restrict__ sids, int N,
-                                   int num_indices, float *__restrict__ out, int out_stride) {
-    const long long total = (long long)num_indices * N;
-    for (long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (long long)gridDim.x * blockDim.x) {
-        const long long i = e / N;
-        out[i * out_stride + sids[e]] = skeys[e];
+                                   int num_indices, int ppb, int num_parts, float *__restrict__ out,
+                                   int out_stride) {
+    const long long nseg = (long long)num_indices * num_parts;
+    for (long long seg = blockIdx.x; seg < nseg; seg += gridDim.x) {
+        const int i = (int)(seg / num_parts), b = (int)(seg % num_parts);
+        const long long lo = (long long)b * ppb;
+        const int n = (int)min((long long)ppb, (long long)N - lo);
+        const size_t row = segment_start(lo, i, num_indices, n);
+        for (int x = threadIdx.x; x < n; x += blockDim.x)
+            out[(size_t)i * out_stride + sids[row + x]] = skeys[row + x];
     }
 }
 

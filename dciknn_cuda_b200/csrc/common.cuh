@@ -465,4 +465,11 @@ __device__ __forceinline__ void topk_slot_close(TopKSlot *s, const CtaTopK &t, c
     __syncthreads();
 }
 
+// Index arrays are partition-major.  First entry of the segment of simple index i for the
+// partition whose first point is `lo` and which holds n points (n = ppb except for the last
+// partition), I simple indices in all.
+__host__ __device__ __forceinline__ size_t segment_start(long long lo, int i, int I, int n) {
+    return (size_t)lo * (size_t)I + (size_t)i * (size_t)n;
+}
+
 }  // namespace dci

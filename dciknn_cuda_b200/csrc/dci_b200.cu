@@ -108,7 +108,7 @@ struct dci_b200 {
     int num_points = 0, P = 0, T = 0, ppb = 0, num_parts = 0;
     const float *d_data = nullptr;       // borrowed
     float *d_proj = nullptr;             // [L*S][dim]
-    Buf keys, ids, pos, keysT;           // [L*S][N] sorted index, inverse positions, stride-T keys
+    Buf keys, ids, pos, keysT;           // sorted index, inverse positions, stride-T keys: L*S*N entries each, partition-major (segment_start)
     Buf tmp_keys, qproj, part_topk, scratch, merge_scratch, stats, phases, hq, hids, hdists;
     int stats_on = 0, stats_nq = 0, phases_valid = 0;
     int timing_on = 0;
@@ -430,10 +430,9 @@ int dci_b200_append(dci_b200_t *h, const float *d_all_data, int num_points_total
     // 1. the old rows' keys, back in id order, at the new row stride
     DCI_CUDA(h->tmp_keys.ensure((size_t)I * n_new * sizeof(float)));
     {
-        const long long total = (long long)I * n_old;
-        const unsigned grid = (unsigned)std::min<long long>((total + 255) / 256, (long long)h->sm_count * 8);
-        dci::unsort_keys_kernel<<<grid, 256, 0, st>>>((const float *)h->keys.p, (const int *)h->ids.p, n_old, I,
-                                                      (float *)h->tmp_keys.p, n_new);
+        const unsigned grid = (unsigned)std::min<long long>((long long)I * h->num_parts, (long long)h->sm_count * 8);
+        dci::unsort_keys_kernel<<<grid, 256, 0, st>>>((const float *)h->keys.p, (const int *)h->ids.p, n_old, I, h->ppb,
+                                                      h->num_parts, (float *)h->tmp_keys.p, n_new);
         h->launches++;
         DCI_CUDA(cudaGetLastError());
     }
@@ -482,17 +481,20 @@ int dci_b200_set_index(dci_b200_t *h, const float *d_data, int num_points, int b
     DCI_CUDA(h->pos.ensure(n_entries * (ppb <= 65535 ? sizeof(uint16_t) : sizeof(uint32_t))));
     DCI_CUDA(h->errflag.ensure(sizeof(int)));
     DCI_CUDA(cudaMemsetAsync(h->errflag.p, 0, sizeof(int), st));
-    DCI_CUDA(cudaMemcpyAsync(h->keys.p, h_keys, n_entries * sizeof(float), cudaMemcpyHostToDevice, st));
-    DCI_CUDA(cudaMemcpyAsync(h->ids.p, h_ids, n_entries * sizeof(int), cudaMemcpyHostToDevice, st));
+    // the caller's arrays are [I][N]; the kernel checks them and writes the partition-major index
+    DCI_CUDA(h->tmp_keys.ensure(n_entries * sizeof(float)));
+    DCI_CUDA(h->scratch.ensure(n_entries * sizeof(int)));
+    DCI_CUDA(cudaMemcpyAsync(h->tmp_keys.p, h_keys, n_entries * sizeof(float), cudaMemcpyHostToDevice, st));
+    DCI_CUDA(cudaMemcpyAsync(h->scratch.p, h_ids, n_entries * sizeof(int), cudaMemcpyHostToDevice, st));
     const unsigned grid = (unsigned)std::min<long long>((long long)I * num_parts, (long long)h->sm_count * 8);
     if (ppb <= 65535)
-        dci::derive_index_kernel<uint16_t><<<grid, 256, 0, st>>>((const float *)h->keys.p, (const int *)h->ids.p, num_points,
-                                                                  I, ppb, num_parts, thread_size, (uint16_t *)h->pos.p,
-                                                                  (float *)h->keysT.p, (int *)h->errflag.p);
+        dci::derive_index_kernel<uint16_t><<<grid, 256, 0, st>>>(
+            (const float *)h->tmp_keys.p, (const int *)h->scratch.p, num_points, I, ppb, num_parts, thread_size,
+            (float *)h->keys.p, (int *)h->ids.p, (uint16_t *)h->pos.p, (float *)h->keysT.p, (int *)h->errflag.p);
     else
-        dci::derive_index_kernel<uint32_t><<<grid, 256, 0, st>>>((const float *)h->keys.p, (const int *)h->ids.p, num_points,
-                                                                  I, ppb, num_parts, thread_size, (uint32_t *)h->pos.p,
-                                                                  (float *)h->keysT.p, (int *)h->errflag.p);
+        dci::derive_index_kernel<uint32_t><<<grid, 256, 0, st>>>(
+            (const float *)h->tmp_keys.p, (const int *)h->scratch.p, num_points, I, ppb, num_parts, thread_size,
+            (float *)h->keys.p, (int *)h->ids.p, (uint32_t *)h->pos.p, (float *)h->keysT.p, (int *)h->errflag.p);
     h->launches++;
     DCI_CUDA(cudaGetLastError());
     int flag = 0;
@@ -682,9 +684,18 @@ int dci_b200_get_index(dci_b200_t *h, float *h_keys, int *h_ids) {
     if (h->num_points <= 0) return fail(DCI_B200_ERR_STATE, "the index is empty");
     DeviceGuard g(h->device);
     DCI_CUDA(cudaDeviceSynchronize());
-    const size_t n = (size_t)h->L * h->S * h->num_points;
-    DCI_CUDA(cudaMemcpy(h_keys, h->keys.p, n * sizeof(float), cudaMemcpyDeviceToHost));
-    DCI_CUDA(cudaMemcpy(h_ids, h->ids.p, n * sizeof(int), cudaMemcpyDeviceToHost));
+    // the index is partition-major on the device; callers see [I][N]
+    const int I = h->L * h->S;
+    const size_t n = (size_t)I * h->num_points;
+    DCI_CUDA(h->tmp_keys.ensure(n * sizeof(float)));
+    DCI_CUDA(h->scratch.ensure(n * sizeof(int)));
+    const unsigned grid = (unsigned)std::min<long long>((long long)I * h->num_parts, (long long)h->sm_count * 8);
+    dci::export_index_kernel<<<grid, 256>>>((const float *)h->keys.p, (const int *)h->ids.p, h->num_points, I, h->ppb,
+                                            h->num_parts, (float *)h->tmp_keys.p, (int *)h->scratch.p);
+    h->launches++;
+    DCI_CUDA(cudaGetLastError());
+    DCI_CUDA(cudaMemcpy(h_keys, h->tmp_keys.p, n * sizeof(float), cudaMemcpyDeviceToHost));
+    DCI_CUDA(cudaMemcpy(h_ids, h->scratch.p, n * sizeof(int), cudaMemcpyDeviceToHost));
     return 0;
 }
 

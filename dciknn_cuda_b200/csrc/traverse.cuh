@@ -39,10 +39,12 @@
 namespace dci {
 
 struct TraverseParams {
-    const float *skeys;        // [I][N] sorted keys
-    const float *skeysT;       // [I][N] the same keys, every segment stride-T transposed
-    const int *sids;           // [I][N] point ids
-    const void *spos;          // [I][N] position of each point in its sorted segment (u16 or u32)
+    // index arrays, partition-major: the segment of (partition b, simple index i) starts at
+    // I * b * ppb + i * n_b, n_b = points of partition b (see segment_start in build_index.cuh)
+    const float *skeys;        // sorted keys
+    const float *skeysT;       // the same keys, every segment stride-T transposed
+    const int *sids;           // point ids
+    const void *spos;          // position of each point in its sorted segment (u16 or u32)
     const float *data;         // [N][dim]
     const float *qproj;        // [I][nq_total]
     const float *query;        // [nq_total][dim]
@@ -340,7 +342,7 @@ traverse_kernel(const TraverseParams prm) {
 
         // ---- 1. split positions: warp-wide 32-ary lower bound per simple index
         for (int i = warp; i < I; i += nw) {
-            const float *keys = prm.skeys + (size_t)i * N + lo;
+            const float *keys = prm.skeys + segment_start(lo, i, I, n);
             const float qv = s_qp[i];
             int lo_ = 0, hi_ = n;
             while (lo_ < hi_) {
@@ -413,7 +415,7 @@ traverse_kernel(const TraverseParams prm) {
                             // cases read the segment's first / last key
                             const int start = g * T - s_cb[i].x;
                             const int at = start < 0 ? 0 : (start >= n ? last_t : s_kt[i] + g);
-                            kv[u] = __ldg(prm.skeysT + (size_t)i * N + lo + at);
+                            kv[u] = __ldg(prm.skeysT + segment_start(lo, i, I, n) + at);
                         }
                     }
 #pragma unroll
@@ -481,7 +483,7 @@ traverse_kernel(const TraverseParams prm) {
                 for (int h = 0; h < S; ++h) {
                     const int i = m * S + h;
                     const int2 cb = s_cb[i];
-                    const PosT *row = spos + (size_t)i * N + lo;
+                    const PosT *row = spos + segment_start(lo, i, I, n);
                     const ValT *rkb = rkm + cb.y;
                     uint32_t y[kPromoPoints];
 #pragma unroll
@@ -501,14 +503,25 @@ traverse_kernel(const TraverseParams prm) {
                 for (int j = 0; j < kPromoPoints; ++j)
                     if ((mx[j] >> prm.tshift) < (best[j] >> prm.tshift)) best[j] = mx[j];   // ties keep the lower composite
             }
+            // one reservation per warp for the lane-0 promotions of all its points (every warp of
+            // the CTA appends to the same counter)
+            unsigned m0[kPromoPoints];
+            int total0 = 0;
 #pragma unroll
             for (int j = 0; j < kPromoPoints; ++j) {
                 const int p = p0 + j * blockDim.x + tid;
                 const bool live = p < n;
                 if (live) kenc[p] = best[j];
-                const bool is0 = live && (best[j] & tmask) == 0u;
-                const int slot0 = warp_append_slot(is0, &s_count[0]);
-                if (is0) list[slot0] = (ValT)(best[j] >> prm.tshift);
+                m0[j] = __ballot_sync(0xFFFFFFFFu, live && (best[j] & tmask) == 0u);
+                total0 += __popc(m0[j]);
+            }
+            int base0 = 0;
+            if (lane == 0 && total0) base0 = atomicAdd(&s_count[0], total0);
+            base0 = __shfl_sync(0xFFFFFFFFu, base0, 0);
+#pragma unroll
+            for (int j = 0; j < kPromoPoints; ++j) {
+                if ((m0[j] >> lane) & 1u) list[base0 + __popc(m0[j] & lanemask_lt())] = (ValT)(best[j] >> prm.tshift);
+                base0 += __popc(m0[j]);
             }
         }
         __syncthreads();
