@@ -22,6 +22,7 @@ SYMBOLS = [
     ("dci_b200_get_proj", C.c_int, [_vp, _vp]),
     ("dci_b200_set_proj", C.c_int, [_vp, _vp]),
     ("dci_b200_add", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, _vp]),
+    ("dci_b200_last_projection_ms", C.c_int, [_vp, C.POINTER(C.c_float)]),
     ("dci_b200_append", C.c_int, [_vp, _vp, C.c_int, _vp]),
     ("dci_b200_blind_width", C.c_int, [C.c_int, C.c_int]),
     ("dci_b200_query_blind", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]),

@@ -368,6 +368,12 @@ class DCI(object):
     def enable_timing(self, on=True):
         _capi.check(_capi.lib().dci_b200_enable_timing(self._live(), 1 if on else 0))
 
+    def last_projection_ms(self):
+        """Device time of the kernels of the last projection that ran with timing on."""
+        ms = C.c_float()
+        _capi.check(_capi.lib().dci_b200_last_projection_ms(self._live(), C.byref(ms)))
+        return float(ms.value)
+
     def get_timing(self):
         """dict of milliseconds spent by the last query per kernel group (timing must be enabled)."""
         buf = (C.c_float * 4)()

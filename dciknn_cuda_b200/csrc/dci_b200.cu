@@ -117,6 +117,8 @@ struct dci_b200 {
     int projection_mode = 0;             // 0: exact fp32 FMA order, 1: tensor cores, 3xTF32
     Buf errflag;
     cudaEvent_t ev[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+    cudaEvent_t pev[2] = {nullptr, nullptr};   // around the kernels of the last projection (timing mode)
+    int pev_valid = 0;
     float t_project = 0.f, t_traverse = 0.f, t_merge = 0.f;
     int t_traverse_launches = 0;
     long long launches = 0;
@@ -136,6 +138,17 @@ int launch_directions(dci_b200 *h, unsigned long long seed, cudaStream_t st) {
 int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cudaStream_t st) {
     if (n <= 0) return 0;
     const int I = h->L * h->S;
+    struct KernelTimer {       // timing mode: events right around the kernel launches, after the host-side set-up
+        dci_b200 *h; cudaStream_t st; bool on;
+        void start() {
+            on = h->timing_on != 0;
+            h->pev_valid = 0;
+            if (!on) return;
+            for (auto &e : h->pev) if (!e && cudaEventCreate(&e) != cudaSuccess) { on = false; return; }
+            cudaEventRecord(h->pev[0], st);
+        }
+        void stop() { if (on && cudaEventRecord(h->pev[1], st) == cudaSuccess) h->pev_valid = 1; }
+    } timer{h, st, false};
     if (h->projection_mode != 0) {
         DCI_CUDA(h->errflag.ensure(sizeof(int)));
         DCI_CUDA(cudaMemsetAsync(h->errflag.p, 0, sizeof(int), st));
@@ -151,6 +164,7 @@ int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cud
             DCI_CUDA(cudaFuncSetAttribute(dci::project_tf32x3_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                           (int)dci::kTcTmaSmem));
         h->last_projection_tma = tma ? 1 : 0;
+        timer.start();
         for (int i0 = 0; i0 < I; i0 += dci::kTcDirs) {
             if (persistent)
                 dci::project_tf32x3_persistent_kernel<<<std::min<unsigned>(tgrid, (unsigned)h->sm_count), dci::kPsThreads,
@@ -165,6 +179,7 @@ int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cud
             h->launches++;
             DCI_CUDA(cudaGetLastError());
         }
+        timer.stop();
         int flag = 0;      // this mode checks its bounded waits before going on
         DCI_CUDA(cudaMemcpyAsync(&flag, h->errflag.p, sizeof(int), cudaMemcpyDeviceToHost, st));
         DCI_CUDA(cudaStreamSynchronize(st));
@@ -172,6 +187,7 @@ int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cud
         return 0;
     }
     const unsigned grid = (unsigned)((n + dci::kProjPoints - 1) / dci::kProjPoints);
+    timer.start();
     // fewest passes over the points, then the smallest accumulator count that achieves it
     if (I <= 8)
         dci::project_exact_kernel<8><<<grid, dci::kProjPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
@@ -183,6 +199,7 @@ int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cud
         dci::project_exact_kernel<30><<<grid, dci::kProjPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
     else
         dci::project_exact_kernel<40><<<grid, dci::kProjPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
+    timer.stop();
     h->launches++;
     DCI_CUDA(cudaGetLastError());
     return 0;
@@ -344,6 +361,7 @@ int dci_b200_destroy(dci_b200_t *h) {
     for (Buf *b : bufs) b->release();
     if (h->d_proj) cudaFree(h->d_proj);
     for (auto &e : h->ev) if (e) cudaEventDestroy(e);
+    for (auto &e : h->pev) if (e) cudaEventDestroy(e);
     delete h;
     return 0;
 }
@@ -761,6 +779,16 @@ int dci_b200_get_timing(dci_b200_t *h, float *h_ms) {
     if (!h_ms) return fail(DCI_B200_ERR_ARG, "h_ms is null");
     h_ms[0] = h->t_project; h_ms[1] = h->t_traverse; h_ms[2] = h->t_merge;
     h_ms[3] = (float)h->t_traverse_launches;
+    return 0;
+}
+
+int dci_b200_last_projection_ms(dci_b200_t *h, float *h_ms) {
+    if (int rc = check_handle(h)) return rc;
+    if (!h_ms) return fail(DCI_B200_ERR_ARG, "h_ms is null");
+    if (!h->pev_valid) return fail(DCI_B200_ERR_STATE, "no projection has run in timing mode yet");
+    DeviceGuard g(h->device);
+    DCI_CUDA(cudaEventSynchronize(h->pev[1]));
+    DCI_CUDA(cudaEventElapsedTime(h_ms, h->pev[0], h->pev[1]));
     return 0;
 }
 

@@ -383,16 +383,36 @@ project_tf32x3_tma_kernel(const __grid_constant__ CUtensorMap map_x, const __gri
 // over 128-point tiles.  Roles:
 //   warp 0, one lane  : producer -- TMA loads of the next 32-coordinate slice (points + directions)
 //                       into a 4-stage ring, as soon as the stage's previous MMAs have drained;
-//   warps 2..5        : converters -- split the landed slice into hi / lo tf32 tiles, then, once a
-//                       tile's last MMAs are committed, read its accumulator from tensor memory and
-//                       store the keys (the accumulator is double buffered, so the MMAs of the next
-//                       tile run during these stores);
+//   warps 2..5        : epilogue -- once a tile's last MMAs are committed, read its accumulator
+//                       from tensor memory and store the keys (the accumulator is double buffered,
+//                       so the MMAs of the next tile run during these stores, and the converters
+//                       never wait for an MMA);
+//   warps 6..13       : converters -- split the landed slice into hi / lo tf32 tiles; eight warps
+//                       with all their loads issued up front, because a conversion is a chain of
+//                       shared-memory round trips and each scheduler only has two of these warps;
 //   warp 1, one lane  : MMA issuer -- 4 x 3 tcgen05.mma per converted slice, committed to the
 //                       stage's "empty" barrier, and after a tile's last slice to "accumulator full".
 // All hand-offs are mbarriers; every wait is bounded and a time-out makes all roles leave.
-constexpr int kPsStages = 4;
-constexpr int kPsThreads = 192;
+constexpr int kPsStages = 5;
+constexpr int kPsThreads = 448;
+constexpr int kPsConverters = 256;
+static_assert(kTcDirs * 8 == kPsConverters && (kTcPoints * 8) % kPsConverters == 0, "converter work split");
 constexpr size_t kPsSmem = kPsStages * kTcStageBytes + 1024;
+
+constexpr uint32_t kPsTmemCols = 256;   // 2 tiles x 3 accumulators x 32 columns, rounded up to a power of two
+
+// 32 consecutive columns of this warp's 32 tensor-memory lanes -> 32 registers per thread
+__device__ __forceinline__ void tmem_ld_32(uint32_t (&r)[32], uint32_t taddr) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -413,14 +433,14 @@ project_tf32x3_persistent_kernel(const __grid_constant__ CUtensorMap map_x, cons
 
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)),
-                     "r"((uint32_t)(2 * kTcDirs)));
+                     "r"((uint32_t)kPsTmemCols));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
     }
     if (tid == 0) {
         abort_flag = 0;
         for (int s_ = 0; s_ < kPsStages; ++s_) {
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&full_bar[s_])));
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], 128;" ::"r"(smem_u32(&conv_bar[s_])));
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&conv_bar[s_])), "r"(kPsConverters));
             asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(smem_u32(&empty_bar[s_])));
         }
         for (int a = 0; a < 2; ++a) {
@@ -468,7 +488,9 @@ project_tf32x3_persistent_kernel(const __grid_constant__ CUtensorMap map_x, cons
             const int a = (int)(t & 1u);
             const uint32_t ause = t >> 1;                 // earlier tiles on this accumulator
             if (ause > 0 && !mbar_wait(smem_u32(&acc_empty[a]), (ause - 1) & 1u)) { abort_flag = 1; break; }
-            const uint32_t tmem_d = tmem_base + (uint32_t)(a * kTcDirs);
+            // three accumulators per tile, one per product kind: MMAs into one accumulator run one
+            // after the other, MMAs into different ones overlap
+            const uint32_t tmem_d = tmem_base + (uint32_t)(a * 3 * kTcDirs);
             for (int c = 0; c < nchunks; ++c, ++q) {
                 const int st = (int)(q % kPsStages);
                 if (!mbar_wait(smem_u32(&conv_bar[st]), (q / kPsStages) & 1u)) { abort_flag = 1; break; }
@@ -478,9 +500,10 @@ project_tf32x3_persistent_kernel(const __grid_constant__ CUtensorMap map_x, cons
 #pragma unroll
                 for (int kk = 0; kk < kTcK / 8; ++kk) {
                     const uint32_t step = kk * 32;
-                    umma_tf32(tmem_d, umma_desc_sw128(al + step), umma_desc_sw128(bh + step), idesc, (c | kk) ? 1u : 0u);
-                    umma_tf32(tmem_d, umma_desc_sw128(ah + step), umma_desc_sw128(bl + step), idesc, 1u);
-                    umma_tf32(tmem_d, umma_desc_sw128(ah + step), umma_desc_sw128(bh + step), idesc, 1u);
+                    const uint32_t acc = (c | kk) ? 1u : 0u;
+                    umma_tf32(tmem_d, umma_desc_sw128(al + step), umma_desc_sw128(bh + step), idesc, acc);
+                    umma_tf32(tmem_d + kTcDirs, umma_desc_sw128(ah + step), umma_desc_sw128(bl + step), idesc, acc);
+                    umma_tf32(tmem_d + 2 * kTcDirs, umma_desc_sw128(ah + step), umma_desc_sw128(bh + step), idesc, acc);
                 }
                 asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
                                  smem_u32(&empty_bar[st]))
@@ -491,49 +514,49 @@ project_tf32x3_persistent_kernel(const __grid_constant__ CUtensorMap map_x, cons
                              smem_u32(&acc_full[a]))
                          : "memory");
         }
-    } else if (warp >= 2) {
-        // ---- converters and epilogue: 128 threads
-        const int ct = tid - 64;
-        uint32_t q = 0, t = 0;
-        for (long long tile = blockIdx.x; tile < ntiles && !abort_flag; tile += gridDim.x, ++t) {
+    } else if (warp >= 6) {
+        // ---- converters
+        const int ct = tid - 192;
+        constexpr int kA4 = kTcPoints * 8 / kPsConverters;      // float4 of the point tile per thread
+        uint32_t q = 0;
+        for (long long tile = blockIdx.x; tile < ntiles && !abort_flag; tile += gridDim.x) {
             for (int c = 0; c < nchunks; ++c, ++q) {
                 const int st = (int)(q % kPsStages);
                 if (!mbar_wait(smem_u32(&full_bar[st]), (q / kPsStages) & 1u)) { abort_flag = 1; break; }
                 unsigned char *sb = base + (size_t)st * kTcStageBytes;
                 float4 *a_hi = reinterpret_cast<float4 *>(sb), *a_lo = reinterpret_cast<float4 *>(sb + kTcPoints * 128);
-                for (int f = ct; f < kTcPoints * 8; f += 128) {
-                    const float4 v = a_hi[f];
-                    float4 h, l;
-                    split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
-                    a_hi[f] = h; a_lo[f] = l;
-                }
                 float4 *b_hi = reinterpret_cast<float4 *>(sb + 2 * kTcPoints * 128);
                 float4 *b_lo = reinterpret_cast<float4 *>(sb + 2 * kTcPoints * 128 + kTcDirs * 128);
-                for (int f = ct; f < kTcDirs * 8; f += 128) {
-                    const float4 v = b_hi[f];
+                float4 v[kA4 + 1];
+#pragma unroll
+                for (int u = 0; u < kA4; ++u) v[u] = a_hi[ct + u * kPsConverters];
+                v[kA4] = b_hi[ct];                               // kTcDirs * 8 == kPsConverters
+#pragma unroll
+                for (int u = 0; u <= kA4; ++u) {
                     float4 h, l;
-                    split_tf32(v.x, h.x, l.x); split_tf32(v.y, h.y, l.y); split_tf32(v.z, h.z, l.z); split_tf32(v.w, h.w, l.w);
-                    b_hi[f] = h; b_lo[f] = l;
+                    split_tf32(v[u].x, h.x, l.x); split_tf32(v[u].y, h.y, l.y);
+                    split_tf32(v[u].z, h.z, l.z); split_tf32(v[u].w, h.w, l.w);
+                    if (u < kA4) { a_hi[ct + u * kPsConverters] = h; a_lo[ct + u * kPsConverters] = l; }
+                    else { b_hi[ct] = h; b_lo[ct] = l; }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 mbar_arrive(smem_u32(&conv_bar[st]));
             }
             if (abort_flag) break;
+        }
+    } else if (warp >= 2) {
+        // ---- epilogue: 128 threads; warp w reads the tensor-memory lanes 32 * (w % 4) .. + 31
+        uint32_t t = 0;
+        for (long long tile = blockIdx.x; tile < ntiles && !abort_flag; tile += gridDim.x, ++t) {
             // epilogue of this tile
             const int a = (int)(t & 1u);
             if (!mbar_wait(smem_u32(&acc_full[a]), (t >> 1) & 1u)) { abort_flag = 1; break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            uint32_t r[32];
-            const uint32_t taddr = tmem_base + (uint32_t)(a * kTcDirs) + ((uint32_t)((warp & 3) * 32) << 16);
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32"
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
-                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                  "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                : "r"(taddr));
+            uint32_t r[32], r1[32], r2[32];
+            const uint32_t taddr = tmem_base + (uint32_t)(a * 3 * kTcDirs) + ((uint32_t)((warp & 3) * 32) << 16);
+            tmem_ld_32(r, taddr);                    // lo x hi
+            tmem_ld_32(r1, taddr + kTcDirs);         // hi x lo
+            tmem_ld_32(r2, taddr + 2 * kTcDirs);     // hi x hi
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(smem_u32(&acc_empty[a]));
@@ -541,7 +564,9 @@ project_tf32x3_persistent_kernel(const __grid_constant__ CUtensorMap map_x, cons
             if (p < n) {
 #pragma unroll
                 for (int cidx = 0; cidx < kTcDirs; ++cidx)
-                    if (i0 + cidx < num_indices) out[(size_t)(i0 + cidx) * n + p] = __uint_as_float(r[cidx]);
+                    if (i0 + cidx < num_indices)     // small terms first
+                        out[(size_t)(i0 + cidx) * n + p] =
+                            (__uint_as_float(r[cidx]) + __uint_as_float(r1[cidx])) + __uint_as_float(r2[cidx]);
             }
         }
     }
@@ -549,7 +574,7 @@ project_tf32x3_persistent_kernel(const __grid_constant__ CUtensorMap map_x, cons
     __syncthreads();
     if (tid == 0 && abort_flag) atomicExch(error, 1);
     if (warp == 0) {
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)(2 * kTcDirs)));
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kPsTmemCols));
     }
 }
 

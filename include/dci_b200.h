@@ -208,6 +208,9 @@ int dci_b200_set_projection(dci_b200_t *h, int mode);
  * has no timers (example.py:74-84 prints wall-clock deltas). */
 int dci_b200_enable_timing(dci_b200_t *h, int on);
 int dci_b200_get_timing(dci_b200_t *h, float *h_ms);
+/* Device time of the kernels of the most recent projection (data or queries) that ran while
+ * timing was on, without the host-side set-up before them. */
+int dci_b200_last_projection_ms(dci_b200_t *h, float *h_ms);
 
 /* Replaces the merge of MDCI.query (dciknn_cuda/core.py:146-157): merges D
  * per-shard result lists, each [num_queries][k] ascending, into the k smallest
