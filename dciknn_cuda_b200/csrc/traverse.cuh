@@ -73,6 +73,7 @@ struct TraverseParams {
 };
 
 constexpr int kMaxQBatch = 8;                  // queries whose exhaustive distance phases share row loads
+constexpr int kPriWidth = 5;                   // simple indices whose window keys a thread loads together
 constexpr int kPromoPoints = 5;                // points a thread carries through the promotion phase
 constexpr int kDistChunk = 16;                 // floats of a row staged per step of the distance phase
 constexpr int kDistStride = kDistChunk + 4;    // padded row stride of the staging tile (floats)
@@ -403,11 +404,11 @@ traverse_kernel(const TraverseParams prm) {
             DCI_PHASE_MARK(10)
             const int gmax = prm.wcap / S;                  // no simple index has more windows than this
             const int last_t = ((n - 1) % T) * (n / T) + min((n - 1) % T, n % T) + (n - 1) / T;
-            for (int h0 = 0; h0 < S; h0 += 4) {
+            for (int h0 = 0; h0 < S; h0 += kPriWidth) {
                 for (int g = tid; g < gmax; g += blockDim.x) {
-                    float kv[4];
+                    float kv[kPriWidth];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
+                    for (int u = 0; u < kPriWidth; ++u) {
                         const int i = m * S + h0 + u;
                         kv[u] = 0.0f;
                         if (h0 + u < S && g < s_cnt[i]) {
@@ -419,7 +420,7 @@ traverse_kernel(const TraverseParams prm) {
                         }
                     }
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
+                    for (int u = 0; u < kPriWidth; ++u) {
                         const int i = m * S + h0 + u;
                         if (h0 + u < S && g < s_cnt[i]) {
                             const uint32_t bits = __float_as_uint(fabsf(kv[u] - s_qp[i]));
