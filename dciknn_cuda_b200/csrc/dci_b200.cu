@@ -109,7 +109,8 @@ struct dci_b200 {
     const float *d_data = nullptr;       // borrowed
     float *d_proj = nullptr;             // [L*S][dim]
     Buf keys, ids, pos, keysT;           // sorted index, inverse positions, stride-T keys: L*S*N entries each, partition-major (segment_start)
-    Buf tmp_keys, qproj, part_topk, scratch, merge_scratch, stats, phases, hq, hids, hdists;
+    Buf tmp_keys, qproj, part_topk, scratch, merge_scratch, stats, phases, hq, hids, hdists, qbound;
+    int distance_bound = 1;              // 1: share a per-query distance bound between partitions
     int stats_on = 0, stats_nq = 0, phases_valid = 0;
     int timing_on = 0;
     int last_qbatch = 1;                 // queries per CTA pass of the last traversal launch
@@ -356,7 +357,7 @@ int dci_b200_destroy(dci_b200_t *h) {
     if (!h) return 0;
     DeviceGuard g(h->device);
     cudaDeviceSynchronize();
-    Buf *bufs[] = {&h->keys, &h->ids, &h->pos, &h->keysT, &h->tmp_keys, &h->qproj, &h->part_topk, &h->scratch, &h->merge_scratch, &h->stats, &h->phases, &h->errflag,
+    Buf *bufs[] = {&h->keys, &h->ids, &h->pos, &h->keysT, &h->tmp_keys, &h->qproj, &h->part_topk, &h->scratch, &h->merge_scratch, &h->stats, &h->phases, &h->errflag, &h->qbound,
                    &h->hq, &h->hids, &h->hdists};
     for (Buf *b : bufs) b->release();
     if (h->d_proj) cudaFree(h->d_proj);
@@ -598,9 +599,14 @@ static int query_impl(dci_b200_t *h, const float *d_query, int num_queries, int 
     prm.part_topk = (uint64_t *)h->part_topk.p;
     const int merge_grid_cap = merge_global ? 2 * h->sm_count : (1 << 30);
     if (merge_global) DCI_CUDA(h->merge_scratch.ensure((size_t)merge_grid_cap * 2 * merge_cap * sizeof(uint64_t)));
+    if (h->distance_bound && !blind) DCI_CUDA(h->qbound.ensure(sizeof(uint32_t) * (size_t)batch));
     for (int q0 = 0; q0 < num_queries; q0 += batch) {
         prm.q0 = q0;
         prm.nq = std::min(batch, num_queries - q0);
+        if (h->distance_bound && !blind) {
+            prm.qbound = (uint32_t *)h->qbound.p;
+            DCI_CUDA(cudaMemsetAsync(prm.qbound, 0x7F, sizeof(uint32_t) * (size_t)prm.nq, st));   // 0x7F7F7F7F: a huge finite float
+        }
         if (timing) DCI_CUDA(cudaEventRecord(h->ev[2], st));
         int rc;
         if (prm.ppb <= 65535)

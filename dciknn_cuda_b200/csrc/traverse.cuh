@@ -68,6 +68,8 @@ struct TraverseParams {
     int vec8;                  // rows of data start on 32-byte boundaries: one full sector per load
     int qbatch;                // queries of one partition a CTA takes together (1..kMaxQBatch)
     int dense_cap;             // capacity of the dense pass's selection buffers: power of two >= kpart + blockDim/4
+    uint32_t *qbound;          // nullptr or [nq]: per query of this launch, fp32 bits of an upper bound of its k-th
+                               // smallest distance found so far (any partition); candidates beyond it are dropped
     int blind;                 // 1: no distances; a promoted point's key is its promotion iteration (needs topk_global)
     FastDiv divT;
 };
@@ -171,11 +173,15 @@ __device__ __forceinline__ float dist_sequential(const float *__restrict__ row, 
 // 32-byte sector of its own row (sm_100 has 256-bit global loads), so no bytes
 // are fetched that the lane does not use and no shared staging is needed.
 // Requires dim % 8 == 0 and rows on 32-byte boundaries.
-__device__ __forceinline__ float dist_sequential_v8(const float *__restrict__ row, const float *qv, int dim) {
+// The partial sums only grow (every term is a square), so a row is abandoned -- the rest of it is
+// not even loaded -- as soon as its sum exceeds bound_sq; the result is then -1.
+__device__ __forceinline__ float dist_sequential_v8(const float *__restrict__ row, const float *qv, int dim,
+                                                    float bound_sq) {
     float sq = 0.0f;
     const int n8 = dim >> 3;
 #pragma unroll 2
     for (int c = 0; c < n8; ++c) {
+        if (sq > bound_sq) return -1.0f;
         float a0, a1, a2, a3, a4, a5, a6, a7;
         asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                      : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3), "=f"(a4), "=f"(a5), "=f"(a6), "=f"(a7)
@@ -555,11 +561,27 @@ traverse_kernel(const TraverseParams prm) {
             lane0_stat = cta_sum(c, s_scratch);
         }
         __syncthreads();
-        for (int p0 = 0; p0 < n; p0 += blockDim.x) {
-            const int p = p0 + tid;
-            const bool take = p < n && (long long)(kenc[p] >> prm.tshift) <= stop;
-            const int sl = warp_append_slot(take, &s_count[1]);
-            if (take) list[sl] = (ValT)p;
+        // candidates = points promoted no later than `stop`; a warp reserves list slots for eight
+        // rounds of its points at once (all warps append to one counter)
+        const uint32_t stop_enc = stop >= (long long)(0xFFFFFFFFu >> prm.tshift) ? 0xFFFFFFFFu
+                                                                                 : (((uint32_t)stop + 1u) << prm.tshift) - 1u;
+        for (int p0 = 0; p0 < n; p0 += 8 * blockDim.x) {
+            unsigned mk[8];
+            int tot = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int p = p0 + j * blockDim.x + tid;
+                mk[j] = __ballot_sync(0xFFFFFFFFu, p < n && kenc[p] <= stop_enc);
+                tot += __popc(mk[j]);
+            }
+            int base = 0;
+            if (lane == 0 && tot) base = atomicAdd(&s_count[1], tot);
+            base = __shfl_sync(0xFFFFFFFFu, base, 0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if ((mk[j] >> lane) & 1u) list[base + __popc(mk[j] & lanemask_lt())] = (ValT)(p0 + j * blockDim.x + tid);
+                base += __popc(mk[j]);
+            }
         }
         __syncthreads();
         const int ncand = s_count[1];
@@ -600,6 +622,19 @@ traverse_kernel(const TraverseParams prm) {
             continue;
         }
         // ---- 5. distances of the promoted points and the partition's top-k
+        // Only the query's k nearest candidates over all partitions reach the result, and the k-th
+        // best of any one partition bounds that distance from above: candidates farther than the
+        // best such bound published so far can be dropped (strictly farther, so ties are kept).
+        // Which partitions have published depends on timing; the merged result does not.
+        float bound_d = __int_as_float(0x7F800000), bound_sq = bound_d;
+        if (prm.qbound && !prm.blind) {
+            const uint32_t bb = *reinterpret_cast<volatile uint32_t *>(prm.qbound + ql);
+            if (bb < 0x7F7F7F7Fu) {                                  // the buffer starts as 0x7F7F7F7F: no bound yet
+                bound_d = __uint_as_float(bb);
+                const float up = __uint_as_float(bb + 1u);           // next float above the bound
+                bound_sq = __fmul_ru(up, up);                        // sq > bound_sq  =>  sqrt(sq) > bound_d
+            }
+        }
         CtaTopK topk;
         topk.init(topk_bufs, &s_count[0], &s_thresh, s_sel, s_res, prm.topk_cap, prm.kpart);
         for (int base = 0; base < ncand; base += blockDim.x) {
@@ -613,17 +648,17 @@ traverse_kernel(const TraverseParams prm) {
             } else if (prm.vec8) {
                 if (j < ncand) {
                     const long long gid = lo + (long long)list[j];
-                    const float d = dist_sequential_v8(prm.data + (size_t)gid * dim, qvec, dim);
-                    key = ((uint64_t)__float_as_uint(d) << 32) | (uint32_t)gid;
+                    const float d = dist_sequential_v8(prm.data + (size_t)gid * dim, qvec, dim, bound_sq);
+                    if (d >= 0.0f && d <= bound_d) key = ((uint64_t)__float_as_uint(d) << 32) | (uint32_t)gid;
                 }
             } else if (SMEM && prm.vec4) {
                 const long long gid = lo + (long long)list[j < ncand ? j : 0];
                 const float d = dist_rows_tiled(prm.data, gid, qvec, dim, tiles + warp * (32 * kDistStride));
-                if (j < ncand) key = ((uint64_t)__float_as_uint(d) << 32) | (uint32_t)gid;
+                if (j < ncand && d <= bound_d) key = ((uint64_t)__float_as_uint(d) << 32) | (uint32_t)gid;
             } else if (j < ncand) {
                 const long long gid = lo + (long long)list[j];
                 const float d = dist_sequential(prm.data + (size_t)gid * dim, qvec, dim, prm.vec4);
-                key = ((uint64_t)__float_as_uint(d) << 32) | (uint32_t)gid;
+                if (d <= bound_d) key = ((uint64_t)__float_as_uint(d) << 32) | (uint32_t)gid;
             }
             DCI_PHASE_MARK(5)
             topk.offer(key);
@@ -633,6 +668,8 @@ traverse_kernel(const TraverseParams prm) {
         uint64_t *out = prm.part_topk + ((size_t)ql * prm.num_parts + b) * prm.kpart;
         const uint64_t *res = topk.result();
         for (int j = tid; j < prm.kpart; j += blockDim.x) out[j] = res[j];
+        if (tid == 0 && prm.qbound && !prm.blind && prm.kpart == prm.knn && res[prm.knn - 1] != kEmptySlot)
+            atomicMin(prm.qbound + ql, (uint32_t)(res[prm.knn - 1] >> 32));
         __syncthreads();
         DCI_PHASE_MARK(6)
         if (prm.phase_cycles && tid == 0) atomicAdd((unsigned long long *)&prm.phase_cycles[15], 1ull);
