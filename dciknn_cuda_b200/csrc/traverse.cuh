@@ -285,6 +285,7 @@ traverse_kernel(const TraverseParams prm) {
     __shared__ int s_count[2];
     __shared__ uint64_t s_thresh;
     __shared__ TopKSlot s_slot[kMaxQBatch];  // dense distance phase: one top-k per deferred query
+    __shared__ float s_bd[kMaxQBatch], s_bsq[kMaxQBatch];   // ... and its distance bound (plain and squared)
     __shared__ int s_dense[kMaxQBatch];      // local query numbers deferred to the dense phase
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
@@ -684,7 +685,19 @@ traverse_kernel(const TraverseParams prm) {
         for (int t = 0; t < ndense; ++t) {
             const float *src = prm.query + (size_t)(prm.q0 + s_dense[t]) * dim;
             for (int c = tid; c < dim; c += blockDim.x) dq[(size_t)t * dim + c] = src[c];
-            if (tid == 0) { s_slot[t].count = 0; s_slot[t].half = 0; s_slot[t].thresh = kEmptySlot; }
+            if (tid == 0) {
+                s_slot[t].count = 0; s_slot[t].half = 0; s_slot[t].thresh = kEmptySlot;
+                float bd = __int_as_float(0x7F800000), bsq = bd;     // the query's bound, as in phase 5
+                if (prm.qbound) {
+                    const uint32_t bb = *reinterpret_cast<volatile uint32_t *>(prm.qbound + s_dense[t]);
+                    if (bb < 0x7F7F7F7Fu) {
+                        bd = __uint_as_float(bb);
+                        const float up = __uint_as_float(bb + 1u);
+                        bsq = __fmul_ru(up, up);
+                    }
+                }
+                s_bd[t] = bd; s_bsq[t] = bsq;
+            }
         }
         __syncthreads();
         const int n8 = dim >> 3;
@@ -697,13 +710,19 @@ traverse_kernel(const TraverseParams prm) {
             if (live) {
                 const float *row = prm.data + (size_t)(lo + r) * dim;
                 for (int c = 0; c < n8; ++c) {
+                    if ((c & 3) == 0 && c) {     // every 32 coordinates: is the row still within some query's bound?
+                        bool any = false;
+#pragma unroll
+                        for (int t = 0; t < kMaxQBatch; ++t) any |= (t < ndense && sq[t] <= s_bsq[t]);
+                        if (!any) break;
+                    }
                     float a0, a1, a2, a3, a4, a5, a6, a7;
                     asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
                                  : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3), "=f"(a4), "=f"(a5), "=f"(a6), "=f"(a7)
                                  : "l"(row + c * 8));
 #pragma unroll
                     for (int t = 0; t < kMaxQBatch; ++t) {
-                        if (t < ndense) {
+                        if (t < ndense && sq[t] <= s_bsq[t]) {   // a sum beyond the bound stays there
                             const float4 b0 = *reinterpret_cast<const float4 *>(dq + (size_t)t * dim + c * 8);
                             const float4 b1 = *reinterpret_cast<const float4 *>(dq + (size_t)t * dim + c * 8 + 4);
                             float s_ = sq[t], d;
@@ -729,8 +748,9 @@ traverse_kernel(const TraverseParams prm) {
                 if (t < ndense) {
                     uint64_t *bufs = reinterpret_cast<uint64_t *>(big + (size_t)t * tk_bytes);
                     CtaTopK topk = topk_slot_open(&s_slot[t], bufs, s_sel, s_res, prm.dense_cap, prm.kpart);
-                    const uint64_t key = live ? (((uint64_t)__float_as_uint(__fsqrt_rn(sq[t])) << 32) | (uint32_t)(lo + r))
-                                              : kEmptySlot;
+                    const float dfin = __fsqrt_rn(sq[t]);
+                    const uint64_t key = (live && sq[t] <= s_bsq[t] && dfin <= s_bd[t])
+                                             ? (((uint64_t)__float_as_uint(dfin) << 32) | (uint32_t)(lo + r)) : kEmptySlot;
                     for (int part = 0; part < 4; ++part)
                         topk.offer_from((tid / quarter) == part ? key : kEmptySlot, quarter);
                     topk_slot_close(&s_slot[t], topk, bufs);
@@ -745,6 +765,8 @@ traverse_kernel(const TraverseParams prm) {
             uint64_t *out = prm.part_topk + ((size_t)s_dense[t] * prm.num_parts + b) * prm.kpart;
             const uint64_t *res = topk.result();
             for (int j = tid; j < prm.kpart; j += blockDim.x) out[j] = res[j];
+            if (tid == 0 && prm.qbound && prm.kpart == prm.knn && res[prm.knn - 1] != kEmptySlot)
+                atomicMin(prm.qbound + s_dense[t], (uint32_t)(res[prm.knn - 1] >> 32));
             __syncthreads();
         }
         DCI_PHASE_MARK(6)
