@@ -175,29 +175,45 @@ __device__ __forceinline__ float dist_sequential(const float *__restrict__ row, 
 // Requires dim % 8 == 0 and rows on 32-byte boundaries.
 // The partial sums only grow (every term is a square), so a row is abandoned -- the rest of it is
 // not even loaded -- as soon as its sum exceeds bound_sq; the result is then -1.
+__device__ __forceinline__ void ld_row8(const float *p, float (&a)[8]) {
+    asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(a[0]), "=f"(a[1]), "=f"(a[2]), "=f"(a[3]), "=f"(a[4]), "=f"(a[5]), "=f"(a[6]), "=f"(a[7])
+                 : "l"(p));
+}
+__device__ __forceinline__ float sq_accumulate8(float sq, const float (&a)[8], const float *q) {
+    const float4 b0 = *reinterpret_cast<const float4 *>(q);
+    const float4 b1 = *reinterpret_cast<const float4 *>(q + 4);
+    float d = __fsub_rn(a[0], b0.x); sq = __fmaf_rn(d, d, sq);
+    d = __fsub_rn(a[1], b0.y); sq = __fmaf_rn(d, d, sq);
+    d = __fsub_rn(a[2], b0.z); sq = __fmaf_rn(d, d, sq);
+    d = __fsub_rn(a[3], b0.w); sq = __fmaf_rn(d, d, sq);
+    d = __fsub_rn(a[4], b1.x); sq = __fmaf_rn(d, d, sq);
+    d = __fsub_rn(a[5], b1.y); sq = __fmaf_rn(d, d, sq);
+    d = __fsub_rn(a[6], b1.z); sq = __fmaf_rn(d, d, sq);
+    d = __fsub_rn(a[7], b1.w); sq = __fmaf_rn(d, d, sq);
+    return sq;
+}
 __device__ __forceinline__ float dist_sequential_v8(const float *__restrict__ row, const float *qv, int dim,
                                                     float bound_sq) {
     float sq = 0.0f;
     const int n8 = dim >> 3;
-#pragma unroll 2
-    for (int c = 0; c < n8; ++c) {
+    int c = 0;
+    // two loads in flight per check: a check after every load would expose one memory latency per
+    // 8 coordinates, and four loads do not fit the register budget
+    for (; c + 2 <= n8; c += 2) {
         if (sq > bound_sq) return -1.0f;
-        float a0, a1, a2, a3, a4, a5, a6, a7;
-        asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                     : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3), "=f"(a4), "=f"(a5), "=f"(a6), "=f"(a7)
-                     : "l"(row + c * 8));
-        const float4 b0 = *reinterpret_cast<const float4 *>(qv + c * 8);
-        const float4 b1 = *reinterpret_cast<const float4 *>(qv + c * 8 + 4);
-        float d = __fsub_rn(a0, b0.x); sq = __fmaf_rn(d, d, sq);
-        d = __fsub_rn(a1, b0.y); sq = __fmaf_rn(d, d, sq);
-        d = __fsub_rn(a2, b0.z); sq = __fmaf_rn(d, d, sq);
-        d = __fsub_rn(a3, b0.w); sq = __fmaf_rn(d, d, sq);
-        d = __fsub_rn(a4, b1.x); sq = __fmaf_rn(d, d, sq);
-        d = __fsub_rn(a5, b1.y); sq = __fmaf_rn(d, d, sq);
-        d = __fsub_rn(a6, b1.z); sq = __fmaf_rn(d, d, sq);
-        d = __fsub_rn(a7, b1.w); sq = __fmaf_rn(d, d, sq);
+        float a[8], b[8];
+        ld_row8(row + c * 8, a);
+        ld_row8(row + c * 8 + 8, b);
+        sq = sq_accumulate8(sq, a, qv + c * 8);
+        sq = sq_accumulate8(sq, b, qv + c * 8 + 8);
     }
-    return __fsqrt_rn(sq);
+    if (c < n8 && !(sq > bound_sq)) {
+        float a[8];
+        ld_row8(row + c * 8, a);
+        sq = sq_accumulate8(sq, a, qv + c * 8);
+    }
+    return sq > bound_sq ? -1.0f : __fsqrt_rn(sq);
 }
 
 // Same distances for 32 rows at a time by one warp: lane r owns row r.  The
