@@ -39,8 +39,10 @@ def _nvcc(kernel_src, util_src, include_dir, out):
 
 def build_reference(ref_root=None, force=False):
     """Returns the list of libraries built, or [] when the reference checkout is absent.
-    ref_root defaults to $DCI_REFERENCE_ROOT, else the build machine's mount point."""
-    ref_root = ref_root or os.environ.get("DCI_REFERENCE_ROOT", "/root/reference")
+    ref_root defaults to $DCI_REFERENCE_ROOT, else a checkout named `reference` next to this
+    repository."""
+    sibling = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    ref_root = ref_root or os.environ.get("DCI_REFERENCE_ROOT", sibling)
     ksrc = os.path.join(ref_root, "src", "dci_cuda_kernel.cu")
     usrc = os.path.join(ref_root, "src", "util_kernel.cu")
     inc = os.path.join(ref_root, "include")
