@@ -60,7 +60,7 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one traversal launch from an ncu capture
 # (profiles/traverse_kernel_configs1.md).  The index and the rows are read about once per launch and
 # everything else hits L2, so the figure does not grow with the number of queries.
-NCU_DRAM_BYTES_PER_LAUNCH = {"configs1": 737_185_000}
+NCU_DRAM_BYTES_PER_LAUNCH = {"configs1": 723_818_000}
 
 WORKLOAD_LABEL = {"configs1": "configs[1]", "configs2": "configs[2]", "configs3_shard": "configs[3] (one of 8 shards)",
                   "configs4_shard": "configs[4] (one of 8 shards)"}
