@@ -212,7 +212,10 @@ int launch_build(dci_b200 *h, const float *d_unsorted, cudaStream_t st) {
     const int nthreads = h->ppb >= 4096 ? 1024 : (h->ppb >= 1024 ? 512 : 256);
     const auto lay = dci::BuildLayout<ValT>::make(nthreads, h->ppb);
     const long long nseg = (long long)I * h->num_parts;
-    const size_t static_smem = 256;
+    cudaFuncAttributes fa;
+    DCI_CUDA(cudaFuncGetAttributes(&fa, dci::build_segments_kernel<ValT, true>));
+    // the opt-in limit covers static + dynamic shared memory, and the driver reserves 1 KB per CTA
+    const size_t static_smem = fa.sharedSizeBytes + 1024;
     const bool smem = lay.hist_bytes + lay.buf_bytes + static_smem <= h->smem_optin;
     if (smem) {
         auto kern = dci::build_segments_kernel<ValT, true>;
