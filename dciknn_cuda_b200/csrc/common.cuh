@@ -188,14 +188,14 @@ __device__ void cta_radix_sort(uint32_t *kA, ValT *vA, uint32_t *kB, ValT *vB, i
         }
         __syncthreads();
         // hist[w][d] <- number of keys with digit d in warps before w; digit_base[d] <- total of d
-        if (tid < 256) {
+        for (int dg = tid; dg < 256; dg += blockDim.x) {     // CTAs may have fewer than 256 threads
             uint32_t run = 0;
             for (int ww = 0; ww < nw; ++ww) {
-                const uint32_t c = hist[ww * 256 + tid];
-                hist[ww * 256 + tid] = (CntT)run;
+                const uint32_t c = hist[ww * 256 + dg];
+                hist[ww * 256 + dg] = (CntT)run;
                 run += c;
             }
-            digit_base[tid] = run;
+            digit_base[dg] = run;
         }
         __syncthreads();
         cta_exclusive_scan_u32(digit_base, 256, warp_tot);

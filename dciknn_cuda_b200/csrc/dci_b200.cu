@@ -572,7 +572,7 @@ static int query_impl(dci_b200_t *h, const float *d_query, int num_queries, int 
     prm.divT = dci::FastDiv::make((uint32_t)h->T);
     prm.vec4 = (h->dim % 4 == 0) && (((uintptr_t)h->d_data & 15) == 0) && (((uintptr_t)d_query & 15) == 0);
     prm.vec8 = (h->dim % 8 == 0) && (((uintptr_t)h->d_data & 31) == 0);
-    const int nthreads = prm.wcap >= 4096 ? 1024 : (prm.wcap >= 1024 ? 512 : 256);
+    const int nthreads = prm.wcap >= 4096 ? 1024 : (prm.wcap >= 1024 ? 512 : (prm.wcap >= 256 ? 256 : 64));
     prm.blind = blind ? 1 : 0;
     prm.kpart = std::min(out_width, h->ppb);
     prm.topk_cap = next_pow2(prm.kpart + nthreads);

@@ -50,6 +50,9 @@ EDGE_CASES = [
     ("big_k",              900,  16, 2, 3, 3, 10, 700, 5000, 7000,     4, None),
     ("identical_points",   700,  8,  2, 3, 2, 10, 5, 5000,  50,       4, "identical"),
     ("two_clusters_equal", 3000, 8,  2, 4, 1, 10, 5, 5000,  50,       4, "clusters"),
+    # few windows (a small CTA) and two distinct priorities with many ties: the radix-sort fallback
+    ("two_clusters_small",  600, 8,  2, 4, 2, 10, 5, 5000,  50,       4, "clusters"),
+    ("three_values_small",  400, 6,  1, 5, 1,  7, 4, 5000,  40,       4, "round"),
 ]
 
 
