@@ -46,6 +46,8 @@ SYMBOLS = [
     ("dci_b200_query_noalloc", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                          _vp, _vp, _vp]),
     ("dci_b200_merge_shards", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, _c_llp, _vp, _vp, C.c_int, _vp]),
+    ("dci_b200_query_packed", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp]),
+    ("dci_b200_merge_shards_packed", C.c_int, [_vp, C.c_int, C.c_int, C.c_int, _c_llp, _vp, _vp, C.c_int, _vp]),
 ]
 
 ERR_ARG, ERR_STATE, ERR_CUDA, ERR_UNSUPPORTED = 1, 2, 3, 4

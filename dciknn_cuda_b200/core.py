@@ -162,8 +162,16 @@ class DCI(object):
                 store = torch.empty((max(n_new, n_old + n_old // 2), self._dim), dtype=torch.float32, device=data.device)
                 store[:n_old].copy_(self._array[:n_old])
             store[n_old:n_new].copy_(data)
-            _capi.check(_capi.lib().dci_b200_append(self._live(), C.c_void_p(store.data_ptr()), n_new,
-                                                   _stream_ptr(self._device)))
+            try:
+                _capi.check(_capi.lib().dci_b200_append(self._live(), C.c_void_p(store.data_ptr()), n_new,
+                                                       _stream_ptr(self._device)))
+            except Exception:
+                # a failed append may have emptied the handle: follow it instead of keeping stale counts
+                self.num_points = int(_capi.lib().dci_b200_num_points(self._live()))
+                if self.num_points == 0:
+                    self._array = None
+                    self._store = None
+                raise
         self._store = store
         self._array = store[:n_new]
         self.num_points = n_new
@@ -206,6 +214,31 @@ class DCI(object):
             if return_int_ids:
                 return ids, dists
             return ids.to(torch.float32), dists     # the reference returns ids as float32 (dci_cuda.cpp:111)
+
+    def query_packed(self, query, num_neighbours, num_outer_iterations=5000, *, max_num_candidates=None):
+        """The query's result as one [num_queries, k] int64 CUDA tensor of keys
+        (fp32 distance bits << 32 | shard-local id; -1 in unused slots): the form MDCI gathers
+        between GPUs (dci_b200_query_packed).  An index with fewer than k points (or none)
+        answers with what it has."""
+        _query = query.unsqueeze(0) if len(query.shape) < 2 else query
+        self._check_data(_query)
+        self._ensure_positive_integer(num_neighbours)
+        if max_num_candidates is None:
+            max_num_candidates = 10 * num_neighbours
+        nq, k = _query.shape[0], num_neighbours
+        kk = min(k, self.num_points)
+        with torch.cuda.device(self._device):
+            out = torch.empty((nq, kk), dtype=torch.int64, device=_query.device)
+            if kk > 0:
+                _capi.check(_capi.lib().dci_b200_query_packed(
+                    self._live(), C.c_void_p(_query.data_ptr()), nq, kk, int(num_outer_iterations),
+                    int(max_num_candidates), self._block_size, self._thread_size, C.c_void_p(out.data_ptr()),
+                    _stream_ptr(self._device)))
+            if kk < k:
+                full = torch.full((nq, k), -1, dtype=torch.int64, device=_query.device)
+                full[:, :kk] = out
+                out = full
+        return out
 
     def query_noalloc(self, query, ids_out, dists_out, num_outer_iterations=5000, *, max_num_candidates=None):
         """The same query through dci_b200_query_noalloc, for callers that must not
@@ -408,6 +441,24 @@ def merge_shards(ids, dists, offsets, k):
     return out_ids, out_dists
 
 
+def merge_shards_packed(packed, offsets, k):
+    """packed: [D, nq, k] int64 CUDA tensor of DCI.query_packed results; same output as merge_shards."""
+    D, nq, kk = packed.shape
+    assert kk == k and packed.is_cuda and packed.is_contiguous() and packed.dtype == torch.int64
+    dev = packed.device.index
+    out_ids = torch.empty((nq, k), dtype=torch.int64, device=packed.device)
+    out_dists = torch.empty((nq, k), dtype=torch.float32, device=packed.device)
+    offs = (C.c_longlong * D)(*[int(o) for o in offsets])
+    with torch.cuda.device(dev):
+        _capi.check(_capi.lib().dci_b200_merge_shards_packed(
+            C.c_void_p(packed.data_ptr()), D, nq, k, offs, C.c_void_p(out_ids.data_ptr()),
+            C.c_void_p(out_dists.data_ptr()), dev, _stream_ptr(dev)))
+    return out_ids, out_dists
+
+
+PACKED_MAX_K = 1024     # dci_b200_merge_shards_packed's limit; longer lists travel as two tensors
+
+
 class MDCI(object):
     """Prioritized DCI sharded over several GPUs (reference: core.py:110-169).
 
@@ -422,10 +473,11 @@ class MDCI(object):
     """
 
     def __init__(self, dim, num_comp_indices=2, num_simp_indices=7, bs=100, ts=10, devices=[0], *,
-                 process_group=None, seeds=None, projs=None, _local_engine=None, _merge=None):
+                 process_group=None, seeds=None, projs=None, _local_engine=None, _merge=None, _merge_packed=None):
         self._dim = dim
         self._pg = process_group
         self._merge = merge_shards if _merge is None else _merge
+        self._merge_packed = merge_shards_packed if _merge_packed is None else _merge_packed
         self.data_per_device = 0
         if process_group is None:
             self.devices = [_device_index(d) for d in devices]
@@ -449,19 +501,24 @@ class MDCI(object):
                                  proj=None if projs is None else projs[self.rank])]
 
     def add(self, data):
+        # The reference's rule (core.py:122-125) can leave trailing shards without rows (9 points on
+        # 4 devices: 3 + 3 + 3 + 0) and then fails inside its CUDA code; here such a shard stays empty
+        # and contributes nothing to the merge.
         dpd, bounds = shard_bounds(data.shape[0], self.num_devices)
         self.data_per_device = dpd
         if self._pg is None:
             for i, dev in enumerate(self.devices):
                 lo, hi = bounds[i]
-                self.dcis[i].add(data[lo:hi].to(torch.device("cuda", dev)).contiguous())
+                if hi > lo:
+                    self.dcis[i].add(data[lo:hi].to(torch.device("cuda", dev)).contiguous())
         else:
             lo, hi = bounds[self.rank]
-            shard = data[lo:hi]
-            eng = self.dcis[0]
-            if isinstance(eng, DCI):
-                shard = shard.to(eng.device).contiguous()
-            eng.add(shard)
+            if hi > lo:
+                shard = data[lo:hi]
+                eng = self.dcis[0]
+                if isinstance(eng, DCI):
+                    shard = shard.to(eng.device).contiguous()
+                eng.add(shard)
 
     def add_local(self, shard, data_per_device):
         """process_group mode only: index `shard` (this rank's rows, already cut by
@@ -480,30 +537,42 @@ class MDCI(object):
             raise NotImplementedError("blind querying is per index: the retrieval orders of different shards cannot be merged")
         _query = query.unsqueeze(0) if len(query.shape) < 2 else query
         k = num_neighbours
+        offsets = [self.data_per_device * i for i in range(self.num_devices)]
         if self._pg is None:
             ids, dists = [], []
             home = torch.device("cuda", self.devices[0])
+            nq = _query.shape[0]
             for i, dev in enumerate(self.devices):
-                q = _query.to(torch.device("cuda", dev)).contiguous()
-                a, d = self.dcis[i].query(q, k, num_outer_iterations, max_num_candidates=max_num_candidates,
-                                          return_int_ids=True)
+                n_i = self.dcis[i].num_points
+                a = torch.full((nq, k), -1, dtype=torch.int32, device=home)
+                d = torch.full((nq, k), float("inf"), dtype=torch.float32, device=home)
+                if n_i > 0:      # a shard shorter than k (or empty) answers with what it has
+                    q = _query.to(torch.device("cuda", dev)).contiguous()
+                    ai, di = self.dcis[i].query(q, min(k, n_i), num_outer_iterations,
+                                                max_num_candidates=max_num_candidates, return_int_ids=True)
+                    a[:, :ai.shape[1]] = ai.to(home)
+                    d[:, :di.shape[1]] = di.to(home)
                 ids.append(a)
                 dists.append(d)
-            ids = torch.stack([a.to(home) for a in ids]).contiguous()
-            dists = torch.stack([d.to(home) for d in dists]).contiguous()
+            out_ids, out_dists = self._merge(torch.stack(ids).contiguous(), torch.stack(dists).contiguous(), offsets, k)
         else:
             eng = self.dcis[0]
             q = _query.to(eng.device).contiguous() if isinstance(eng, DCI) else _query
-            a, d = eng.query(q, k, num_outer_iterations, max_num_candidates=max_num_candidates, return_int_ids=True)
-            nq = a.shape[0]
-            ids = torch.empty((self.num_devices * nq, k), dtype=a.dtype, device=a.device)
-            dists = torch.empty((self.num_devices * nq, k), dtype=d.dtype, device=d.device)
-            self._dist.all_gather_into_tensor(ids, a.contiguous(), group=self._pg)      # rank-major concatenation
-            self._dist.all_gather_into_tensor(dists, d.contiguous(), group=self._pg)
-            ids = ids.view(self.num_devices, nq, k)
-            dists = dists.view(self.num_devices, nq, k)
-        offsets = [self.data_per_device * i for i in range(self.num_devices)]
-        out_ids, out_dists = self._merge(ids, dists, offsets, k)
+            nq = q.shape[0]
+            if k <= PACKED_MAX_K and hasattr(eng, "query_packed"):
+                # one collective per query batch: every rank's lists as 64-bit (distance, id) keys
+                mine = eng.query_packed(q, k, num_outer_iterations, max_num_candidates=max_num_candidates)
+                packed = torch.empty((self.num_devices * nq, k), dtype=torch.int64, device=mine.device)
+                self._dist.all_gather_into_tensor(packed, mine.contiguous(), group=self._pg)   # rank-major
+                out_ids, out_dists = self._merge_packed(packed.view(self.num_devices, nq, k), offsets, k)
+            else:
+                a, d = eng.query(q, k, num_outer_iterations, max_num_candidates=max_num_candidates, return_int_ids=True)
+                ids = torch.empty((self.num_devices * nq, k), dtype=a.dtype, device=a.device)
+                dists = torch.empty((self.num_devices * nq, k), dtype=d.dtype, device=d.device)
+                self._dist.all_gather_into_tensor(ids, a.contiguous(), group=self._pg)      # rank-major concatenation
+                self._dist.all_gather_into_tensor(dists, d.contiguous(), group=self._pg)
+                out_ids, out_dists = self._merge(ids.view(self.num_devices, nq, k), dists.view(self.num_devices, nq, k),
+                                                 offsets, k)
         if return_int_ids:
             return out_ids, out_dists
         return out_ids.to(torch.float32), out_dists

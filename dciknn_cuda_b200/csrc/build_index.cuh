@@ -110,6 +110,26 @@ __global__ void derive_index_kernel(const float *__restrict__ in_keys, const int
     }
 }
 
+// Second half of the validation of an installed index: every point of a partition must occur exactly
+// once in each of its segments.  The caller fills spos with 0xFF bytes before derive_index_kernel, so
+// a point that no entry named still holds the sentinel (>= n), and a point named twice leaves another
+// one unnamed.  Sets *bad otherwise.  Same segment loop as derive_index_kernel.
+template <typename PosT>
+__global__ void check_index_kernel(const int *__restrict__ sids, const PosT *__restrict__ spos, int N,
+                                   int num_indices, int ppb, int num_parts, int *bad) {
+    const long long nseg = (long long)num_indices * num_parts;
+    for (long long seg = blockIdx.x; seg < nseg; seg += gridDim.x) {
+        const int i = (int)(seg / num_parts), b = (int)(seg % num_parts);
+        const long long lo = (long long)b * ppb;
+        const int n = (int)min((long long)ppb, (long long)N - lo);
+        const size_t row = segment_start(lo, i, num_indices, n);
+        for (int p = threadIdx.x; p < n; p += blockDim.x) {
+            const long long x = (long long)spos[row + p];
+            if (x >= n || (long long)sids[row + x] != lo + p) atomicExch(bad, 1);
+        }
+    }
+}
+
 // Sorted index back to [I][N] arrays: out_keys / out_ids (either may be null) receive the sorted
 // segments in the layout callers see (dci_b200_get_index).
 __global__ void export_index_kernel(const float *__restrict__ skeys, const int *__restrict__ sids, int N,

@@ -136,23 +136,29 @@ int launch_directions(dci_b200 *h, unsigned long long seed, cudaStream_t st) {
     return 0;
 }
 
-int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cudaStream_t st) {
+// flag_word: device word for the tensor-core kernels' bounded-wait flag; nullptr = the handle's own
+// (allocated on first use).  allow_timing = false keeps the timing events (created on first use) out.
+int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cudaStream_t st,
+                   int *flag_word = nullptr, bool allow_timing = true) {
     if (n <= 0) return 0;
     const int I = h->L * h->S;
     struct KernelTimer {       // timing mode: events right around the kernel launches, after the host-side set-up
-        dci_b200 *h; cudaStream_t st; bool on;
+        dci_b200 *h; cudaStream_t st; bool on; bool allow;
         void start() {
-            on = h->timing_on != 0;
+            on = h->timing_on != 0 && allow;
             h->pev_valid = 0;
             if (!on) return;
             for (auto &e : h->pev) if (!e && cudaEventCreate(&e) != cudaSuccess) { on = false; return; }
             cudaEventRecord(h->pev[0], st);
         }
         void stop() { if (on && cudaEventRecord(h->pev[1], st) == cudaSuccess) h->pev_valid = 1; }
-    } timer{h, st, false};
+    } timer{h, st, false, allow_timing};
     if (h->projection_mode != 0) {
-        DCI_CUDA(h->errflag.ensure(sizeof(int)));
-        DCI_CUDA(cudaMemsetAsync(h->errflag.p, 0, sizeof(int), st));
+        if (!flag_word) {
+            DCI_CUDA(h->errflag.ensure(sizeof(int)));
+            flag_word = (int *)h->errflag.p;
+        }
+        DCI_CUDA(cudaMemsetAsync(flag_word, 0, sizeof(int), st));
         const unsigned tgrid = (unsigned)((n + dci::kTcPoints - 1) / dci::kTcPoints);
         CUtensorMap map_x, map_p;
         const bool tma = h->projection_mode != 2 && make_tensor_map_2d(&map_x, d_x, n, h->dim, dci::kTcPoints) &&
@@ -170,19 +176,19 @@ int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cud
             if (persistent)
                 dci::project_tf32x3_persistent_kernel<<<std::min<unsigned>(tgrid, (unsigned)h->sm_count), dci::kPsThreads,
                                                         dci::kPsSmem, st>>>(map_x, map_p, n, h->dim, I, i0, d_out,
-                                                                            (int *)h->errflag.p);
+                                                                            flag_word);
             else if (tma)
                 dci::project_tf32x3_tma_kernel<<<tgrid, dci::kTcPoints, dci::kTcTmaSmem, st>>>(
-                    map_x, map_p, n, h->dim, I, i0, d_out, (int *)h->errflag.p);
+                    map_x, map_p, n, h->dim, I, i0, d_out, flag_word);
             else
                 dci::project_tf32x3_kernel<<<tgrid, dci::kTcPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, i0, d_out,
-                                                                           (int *)h->errflag.p);
+                                                                           flag_word);
             h->launches++;
             DCI_CUDA(cudaGetLastError());
         }
         timer.stop();
         int flag = 0;      // this mode checks its bounded waits before going on
-        DCI_CUDA(cudaMemcpyAsync(&flag, h->errflag.p, sizeof(int), cudaMemcpyDeviceToHost, st));
+        DCI_CUDA(cudaMemcpyAsync(&flag, flag_word, sizeof(int), cudaMemcpyDeviceToHost, st));
         DCI_CUDA(cudaStreamSynchronize(st));
         if (flag) return fail(DCI_B200_ERR_CUDA, "tensor-core projection: a wait on the MMA barrier timed out");
         return 0;
@@ -458,14 +464,25 @@ int dci_b200_append(dci_b200_t *h, const float *d_all_data, int num_points_total
         h->launches++;
         DCI_CUDA(cudaGetLastError());
     }
-    // 2. keys of the new rows only (staged in the stride-T buffer, which step 3 rewrites anyway)
-    DCI_CUDA(cudaStreamSynchronize(st));       // growing a buffer frees it: nothing may still read it
-    DCI_CUDA(h->keysT.ensure((size_t)I * n_new * sizeof(float)));
-    if (int rc = launch_project(h, d_all_data + (size_t)n_old * h->dim, n_add, (float *)h->keysT.p, st)) return rc;
-    DCI_CUDA(cudaMemcpy2DAsync((float *)h->tmp_keys.p + n_old, (size_t)n_new * sizeof(float), h->keysT.p,
-                               (size_t)n_add * sizeof(float), (size_t)n_add * sizeof(float), (size_t)I,
-                               cudaMemcpyDeviceToDevice, st));
-    DCI_CUDA(cudaStreamSynchronize(st));
+    // 2. keys of the new rows only (staged in the stride-T buffer, which step 3 rewrites anyway).
+    // From here on the old index is gone (its stride-T keys are overwritten), so every failure
+    // leaves the handle empty rather than claiming an index it no longer has.
+    auto invalidate = [h](int rc) { h->num_points = 0; h->d_data = nullptr; return rc; };
+#define DCI_CUDA_OR_EMPTY(call)                                                                     \
+    do {                                                                                            \
+        cudaError_t e_ = (call);                                                                    \
+        if (e_ != cudaSuccess)                                                                      \
+            return invalidate(fail(DCI_B200_ERR_CUDA, "%s failed at %s:%d: %s", #call, __FILE__,    \
+                                   __LINE__, cudaGetErrorString(e_)));                              \
+    } while (0)
+    DCI_CUDA_OR_EMPTY(cudaStreamSynchronize(st));       // growing a buffer frees it: nothing may still read it
+    DCI_CUDA_OR_EMPTY(h->keysT.ensure((size_t)I * n_new * sizeof(float)));
+    if (int rc = launch_project(h, d_all_data + (size_t)n_old * h->dim, n_add, (float *)h->keysT.p, st)) return invalidate(rc);
+    DCI_CUDA_OR_EMPTY(cudaMemcpy2DAsync((float *)h->tmp_keys.p + n_old, (size_t)n_new * sizeof(float), h->keysT.p,
+                                        (size_t)n_add * sizeof(float), (size_t)n_add * sizeof(float), (size_t)I,
+                                        cudaMemcpyDeviceToDevice, st));
+    DCI_CUDA_OR_EMPTY(cudaStreamSynchronize(st));
+#undef DCI_CUDA_OR_EMPTY
     // 3. every segment again, for the partition bounds of the new point count
     if (int rc = ensure_index_buffers(h, (size_t)I * n_new, ppb)) { h->num_points = 0; h->d_data = nullptr; return rc; }
     h->num_points = n_new; h->ppb = ppb; h->num_parts = num_parts; h->d_data = d_all_data;
@@ -509,34 +526,44 @@ int dci_b200_set_index(dci_b200_t *h, const float *d_data, int num_points, int b
     DCI_CUDA(cudaMemcpyAsync(h->tmp_keys.p, h_keys, n_entries * sizeof(float), cudaMemcpyHostToDevice, st));
     DCI_CUDA(cudaMemcpyAsync(h->scratch.p, h_ids, n_entries * sizeof(int), cudaMemcpyHostToDevice, st));
     const unsigned grid = (unsigned)std::min<long long>((long long)I * num_parts, (long long)h->sm_count * 8);
-    if (ppb <= 65535)
+    // positions start as a sentinel (all ones, beyond any partition) so that the second kernel sees
+    // every point that no entry of its segment names
+    DCI_CUDA(cudaMemsetAsync(h->pos.p, 0xFF, n_entries * (ppb <= 65535 ? sizeof(uint16_t) : sizeof(uint32_t)), st));
+    if (ppb <= 65535) {
         dci::derive_index_kernel<uint16_t><<<grid, 256, 0, st>>>(
             (const float *)h->tmp_keys.p, (const int *)h->scratch.p, num_points, I, ppb, num_parts, thread_size,
             (float *)h->keys.p, (int *)h->ids.p, (uint16_t *)h->pos.p, (float *)h->keysT.p, (int *)h->errflag.p);
-    else
+        dci::check_index_kernel<uint16_t><<<grid, 256, 0, st>>>((const int *)h->ids.p, (const uint16_t *)h->pos.p,
+                                                               num_points, I, ppb, num_parts, (int *)h->errflag.p);
+    } else {
         dci::derive_index_kernel<uint32_t><<<grid, 256, 0, st>>>(
             (const float *)h->tmp_keys.p, (const int *)h->scratch.p, num_points, I, ppb, num_parts, thread_size,
             (float *)h->keys.p, (int *)h->ids.p, (uint32_t *)h->pos.p, (float *)h->keysT.p, (int *)h->errflag.p);
-    h->launches++;
+        dci::check_index_kernel<uint32_t><<<grid, 256, 0, st>>>((const int *)h->ids.p, (const uint32_t *)h->pos.p,
+                                                               num_points, I, ppb, num_parts, (int *)h->errflag.p);
+    }
+    h->launches += 2;
     DCI_CUDA(cudaGetLastError());
     int flag = 0;
     DCI_CUDA(cudaMemcpyAsync(&flag, h->errflag.p, sizeof(int), cudaMemcpyDeviceToHost, st));
     DCI_CUDA(cudaStreamSynchronize(st));
-    if (flag) return fail(DCI_B200_ERR_ARG, "the index is not valid: a segment is not ascending or holds an id outside its partition");
+    if (flag) return fail(DCI_B200_ERR_ARG, "the index is not valid: a segment is not ascending, holds an id outside its partition, or names a point twice");
     h->num_points = num_points; h->P = block_size; h->T = thread_size; h->ppb = ppb; h->num_parts = num_parts;
     h->d_data = d_data;
     return 0;
 }
 
 // out_width: entries per query in the outputs (num_neighbours, or the candidate list length of a blind query)
+// d_packed: when not null the merged keys (distance bits << 32 | id) go there and d_ids / d_dists are unused
 static int query_impl(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
                       int num_outer_iterations, int max_num_candidates, int blind, int out_width, int block_size,
-                      int thread_size, int *d_ids, float *d_dists, void *stream) {
+                      int thread_size, int *d_ids, float *d_dists, void *stream,
+                      unsigned long long *d_packed = nullptr) {
     if (int rc = check_handle(h)) return rc;
     if (h->num_points <= 0) return fail(DCI_B200_ERR_STATE, "the index is empty; add data first");
     if (num_queries < 0) return fail(DCI_B200_ERR_ARG, "num_queries must not be negative");
     if (num_queries == 0) return 0;
-    if (!d_query || !d_ids || (!d_dists && !blind)) return fail(DCI_B200_ERR_ARG, "null query or output pointer");
+    if (!d_query || (!d_packed && (!d_ids || (!d_dists && !blind)))) return fail(DCI_B200_ERR_ARG, "null query or output pointer");
     if (num_neighbours <= 0) return fail(DCI_B200_ERR_ARG, "num_neighbours must be positive, got %d", num_neighbours);
     if (num_neighbours > h->num_points)
         return fail(DCI_B200_ERR_ARG, "num_neighbours (%d) exceeds the number of indexed points (%d)", num_neighbours, h->num_points);
@@ -622,7 +649,8 @@ static int query_impl(dci_b200_t *h, const float *d_query, int num_queries, int 
         dci::merge_partitions_kernel<<<std::min(prm.nq, merge_grid_cap), merge_threads,
                                        merge_global ? 0 : (size_t)merge_cap * 16, st>>>(
             prm.part_topk, h->num_parts, prm.kpart, out_width, merge_cap, q0, prm.nq,
-            merge_global ? (uint64_t *)h->merge_scratch.p : nullptr, d_ids, d_dists, prm.blind);
+            merge_global ? (uint64_t *)h->merge_scratch.p : nullptr, d_ids, d_dists, prm.blind,
+            reinterpret_cast<uint64_t *>(d_packed));
         h->launches++;
         DCI_CUDA(cudaGetLastError());
         if (timing) {   // timing mode synchronises after every batch; it is off by default
@@ -645,6 +673,14 @@ int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num
         return fail(DCI_B200_ERR_UNSUPPORTED, "blind querying returns lists of another length: use dci_b200_query_blind");
     return query_impl(h, d_query, num_queries, num_neighbours, num_outer_iterations, max_num_candidates, 0,
                       num_neighbours, block_size, thread_size, d_ids, d_dists, stream);
+}
+
+int dci_b200_query_packed(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
+                          int num_outer_iterations, int max_num_candidates, int block_size, int thread_size,
+                          unsigned long long *d_packed, void *stream) {
+    if (!d_packed) return fail(DCI_B200_ERR_ARG, "null output pointer");
+    return query_impl(h, d_query, num_queries, num_neighbours, num_outer_iterations, max_num_candidates, 0,
+                      num_neighbours, block_size, thread_size, nullptr, nullptr, stream, d_packed);
 }
 
 int dci_b200_blind_width(int num_outer_iterations, int max_num_candidates) {
@@ -830,6 +866,32 @@ int dci_b200_merge_shards(const int *d_ids_in, const float *d_dists_in, int num_
     return 0;
 }
 
+int dci_b200_merge_shards_packed(const unsigned long long *d_packed_in, int num_shards, int num_queries, int k,
+                                 const long long *id_offsets, long long *d_ids_out, float *d_dists_out,
+                                 int device, void *stream) {
+    if (!d_packed_in || !id_offsets || !d_ids_out || !d_dists_out)
+        return fail(DCI_B200_ERR_ARG, "null pointer passed to merge_shards_packed");
+    if (num_shards <= 0 || num_shards > 64 || num_queries < 0 || k <= 0)
+        return fail(DCI_B200_ERR_ARG, "merge_shards_packed needs 1..64 shards, num_queries >= 0 and k > 0");
+    if (k > dci::kMaxTopK)
+        return fail(DCI_B200_ERR_UNSUPPORTED, "merge_shards_packed serves k up to %d; use dci_b200_merge_shards above that", dci::kMaxTopK);
+    if (num_queries == 0) return 0;
+    for (int s = 0; s < num_shards; ++s)
+        if (id_offsets[s] < 0 || id_offsets[s] > 0x7FFFFFFFll)
+            return fail(DCI_B200_ERR_UNSUPPORTED, "id offsets must lie in [0, 2^31)");
+    DeviceGuard g(device);
+    if (!g.ok) return fail(DCI_B200_ERR_CUDA, "cannot select device %d", device);
+    dci::ShardOffsets off;
+    memset(&off, 0, sizeof(off));
+    for (int s = 0; s < num_shards; ++s) off.v[s] = id_offsets[s];
+    const int threads = 256, cap = next_pow2(k + threads);
+    dci::merge_shards_packed_kernel<<<num_queries, threads, (size_t)cap * 16, (cudaStream_t)stream>>>(
+        reinterpret_cast<const uint64_t *>(d_packed_in), num_shards, num_queries, k, cap, off, d_ids_out, d_dists_out);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(DCI_B200_ERR_CUDA, "merge_shards_packed launch: %s", cudaGetErrorString(e));
+    return 0;
+}
+
 }  // extern "C"
 
 // ---------------------------------------------------------------------------
@@ -882,15 +944,19 @@ int query_noalloc_impl(dci_b200 *h, dci::TraverseParams prm, int nthreads, unsig
     const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));
     const long long max_grid = std::min<long long>((long long)num_queries * prm.num_parts, (long long)h->sm_count * per_sm);
     const size_t slabs = per_cta * (size_t)max_grid;
-    const size_t per_query = sizeof(uint64_t) * (size_t)prm.num_parts * prm.kpart;
-    if (slabs + per_query > avail)
+    // per query of a pass: its per-partition result lists and its word of the shared distance bound
+    const size_t per_query = sizeof(uint64_t) * (size_t)prm.num_parts * prm.kpart + sizeof(uint32_t);
+    if (slabs + per_query + 256 > avail)
         return fail(DCI_B200_ERR_UNSUPPORTED,
                     "this index and k need %zu bytes of working memory, the built-in scratch of the allocation-free query holds %u",
-                    slabs + per_query + ((size_t)DCI_B200_NOALLOC_SCRATCH_BYTES - avail), (unsigned)DCI_B200_NOALLOC_SCRATCH_BYTES);
-    const int batch = (int)std::min<size_t>((size_t)num_queries, (avail - slabs) / per_query);
+                    slabs + per_query + 256 + ((size_t)DCI_B200_NOALLOC_SCRATCH_BYTES - avail), (unsigned)DCI_B200_NOALLOC_SCRATCH_BYTES);
+    const int batch = (int)std::min<size_t>((size_t)num_queries, (avail - slabs - 256) / per_query);
     prm.gscratch = scratch;
     prm.gscratch_per_cta = per_cta;
     prm.part_topk = (uint64_t *)(scratch + slabs);
+    uint32_t *qbound = h->distance_bound
+                           ? (uint32_t *)(scratch + slabs + align256(sizeof(uint64_t) * (size_t)prm.num_parts * prm.kpart * batch))
+                           : nullptr;
     const int merge_threads = 256;
     const int merge_cap = next_pow2(prm.knn + merge_threads);
     if (smem) DCI_CUDA(cudaFuncSetAttribute(dci::traverse_kernel<ValT, PosT, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
@@ -898,6 +964,10 @@ int query_noalloc_impl(dci_b200 *h, dci::TraverseParams prm, int nthreads, unsig
     for (int q0 = 0; q0 < num_queries; q0 += batch) {
         prm.q0 = q0;
         prm.nq = std::min(batch, num_queries - q0);
+        if (qbound) {      // the bound words must start as "no bound yet": the array keeps the last call's contents
+            prm.qbound = qbound;
+            DCI_CUDA(cudaMemsetAsync(qbound, 0x7F, sizeof(uint32_t) * (size_t)prm.nq, st));
+        }
         const unsigned grid = (unsigned)std::min<long long>((long long)prm.nq * prm.num_parts, max_grid);
         if (smem) dci::traverse_kernel<ValT, PosT, true, false><<<grid, nthreads, dyn, st>>>(prm);
         else dci::traverse_kernel<ValT, PosT, false, false><<<grid, nthreads, dyn, st>>>(prm);
@@ -935,12 +1005,14 @@ extern "C" int dci_b200_query_noalloc(dci_b200_t *h, const float *d_query, int n
     if (int rc = noalloc_scratch_address(h->device, &scratch)) return rc;
     cudaStream_t st = (cudaStream_t)stream;
     const int I = h->L * h->S;
+    // layout of the array: [flag word of the tensor-core projection, 256 B][projected queries][slabs][lists][bounds]
     const size_t qproj_bytes = align256(sizeof(float) * (size_t)I * num_queries);
-    if (qproj_bytes >= (size_t)DCI_B200_NOALLOC_SCRATCH_BYTES)
+    if (qproj_bytes + 256 >= (size_t)DCI_B200_NOALLOC_SCRATCH_BYTES)
         return fail(DCI_B200_ERR_UNSUPPORTED, "%d queries need %zu bytes for their projections alone, the built-in scratch holds %u",
                     num_queries, qproj_bytes, (unsigned)DCI_B200_NOALLOC_SCRATCH_BYTES);
-    float *qproj = (float *)scratch;
-    if (int rc = launch_project(h, d_query, num_queries, qproj, st)) return rc;
+    float *qproj = (float *)(scratch + 256);
+    // the handle's own flag word and timing events are created on first use, so neither is used here
+    if (int rc = launch_project(h, d_query, num_queries, qproj, st, (int *)scratch, false)) return rc;
 
     dci::TraverseParams prm;
     memset(&prm, 0, sizeof(prm));
@@ -956,11 +1028,12 @@ extern "C" int dci_b200_query_noalloc(dci_b200_t *h, const float *d_query, int n
     while ((1 << prm.tshift) < h->T) ++prm.tshift;
     prm.divT = dci::FastDiv::make((uint32_t)h->T);
     prm.vec4 = (h->dim % 4 == 0) && (((uintptr_t)h->d_data & 15) == 0) && (((uintptr_t)d_query & 15) == 0);
-    const int nthreads = prm.wcap >= 4096 ? 1024 : (prm.wcap >= 1024 ? 512 : 256);
+    prm.vec8 = (h->dim % 8 == 0) && (((uintptr_t)h->d_data & 31) == 0);
+    const int nthreads = prm.wcap >= 4096 ? 1024 : (prm.wcap >= 1024 ? 512 : (prm.wcap >= 256 ? 256 : 64));
     prm.kpart = std::min(num_neighbours, h->ppb);
     prm.topk_cap = next_pow2(prm.kpart + nthreads);
-    unsigned char *rest = scratch + qproj_bytes;
-    const size_t avail = (size_t)DCI_B200_NOALLOC_SCRATCH_BYTES - qproj_bytes;
+    unsigned char *rest = scratch + 256 + qproj_bytes;
+    const size_t avail = (size_t)DCI_B200_NOALLOC_SCRATCH_BYTES - 256 - qproj_bytes;
     if (prm.ppb <= 65535)
         return (prm.wcap <= 65535)
                    ? query_noalloc_impl<uint16_t, uint16_t>(h, prm, nthreads, rest, avail, num_queries, d_ids, d_dists, st)

@@ -797,9 +797,12 @@ traverse_kernel(const TraverseParams prm) {
 // CTA's slab of `gbufs` (2 * topk_cap entries each).
 // blind: the high word of a key is a promotion iteration; out_dists then receives int32 values
 // (-1 in empty slots) and may be null.
+// out_packed (may be null; then out_ids is written): the merged keys themselves, (fp32 distance bits
+// << 32 | id), kEmptySlot in unused slots -- the form in which MDCI ships a shard's lists.
 __global__ void merge_partitions_kernel(const uint64_t *__restrict__ part_topk, int num_parts, int kpart,
                                         int knn, int topk_cap, int q0, int nq, uint64_t *gbufs,
-                                        int *__restrict__ out_ids, float *__restrict__ out_dists, int blind) {
+                                        int *__restrict__ out_ids, float *__restrict__ out_dists, int blind,
+                                        uint64_t *__restrict__ out_packed = nullptr) {
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     __shared__ int s_count;
     __shared__ uint64_t s_thresh;
@@ -820,6 +823,7 @@ __global__ void merge_partitions_kernel(const uint64_t *__restrict__ part_topk, 
         for (int j = threadIdx.x; j < knn; j += blockDim.x) {
             const uint64_t key = buf[j];
             const size_t o = (size_t)(q0 + ql) * knn + j;
+            if (out_packed) { out_packed[o] = key; continue; }
             if (key == kEmptySlot) {
                 out_ids[o] = -1;
                 if (out_dists) out_dists[o] = blind ? __int_as_float(-1) : __int_as_float(0x7F800000);
@@ -860,6 +864,46 @@ __global__ void merge_shards_kernel(const int *__restrict__ ids_in, const float 
                 const float d = dists_in[src];
                 key = ((uint64_t)__float_as_uint(d) << 32) | (uint32_t)((long long)id + offsets.v[s]);
             }
+        }
+        topk.offer(key);
+    }
+    topk.finish();
+    const uint64_t *buf = topk.result();
+    for (int j = threadIdx.x; j < k; j += blockDim.x) {
+        const uint64_t key = buf[j];
+        const size_t o = (size_t)q * k + j;
+        if (key == kEmptySlot) {
+            out_ids[o] = -1;
+            out_dists[o] = __int_as_float(0x7F800000);
+        } else {
+            out_ids[o] = (long long)(uint32_t)key;
+            out_dists[o] = __uint_as_float((uint32_t)(key >> 32));
+        }
+    }
+}
+
+// The same merge for shard lists in packed form (merge_partitions_kernel's out_packed): in is
+// [num_shards][nq][k] keys, local id in the low word.  One CTA per query.
+__global__ void merge_shards_packed_kernel(const uint64_t *__restrict__ in, int num_shards, int nq, int k, int topk_cap,
+                                           const ShardOffsets offsets, long long *__restrict__ out_ids,
+                                           float *__restrict__ out_dists) {
+    extern __shared__ __align__(16) unsigned char dyn_smem[];
+    __shared__ int s_count;
+    __shared__ uint64_t s_thresh;
+    __shared__ uint32_t s_sel[2][256];
+    __shared__ uint32_t s_res[4];
+    const int q = blockIdx.x;
+    const long long total = (long long)num_shards * k;
+    CtaTopK topk;
+    topk.init(reinterpret_cast<uint64_t *>(dyn_smem), &s_count, &s_thresh, s_sel, s_res, topk_cap, k);
+    for (long long base = 0; base < total; base += blockDim.x) {
+        const long long j = base + threadIdx.x;
+        uint64_t key = kEmptySlot;
+        if (j < total) {
+            const int s = (int)(j / k), r = (int)(j % k);
+            const uint64_t v = in[((size_t)s * nq + q) * k + r];
+            if (v != kEmptySlot)
+                key = (v & 0xFFFFFFFF00000000ull) | (uint32_t)((long long)(uint32_t)v + offsets.v[s]);
         }
         topk.offer(key);
     }

@@ -21,6 +21,16 @@
  * stream).  Unless stated otherwise calls are asynchronous with respect to the
  * host: results are complete when the stream reaches the end of the enqueued
  * work.
+ *
+ * Concurrency: a handle owns one set of work buffers (projected queries,
+ * per-partition lists, slabs, statistics) that grow on demand and are reused by
+ * every call.  At most one call per handle may be in flight: use one stream per
+ * handle (or order the streams yourself), and do not call a handle from two
+ * threads at once.  Growing a buffer frees the old one, so a call that needs
+ * more room than any before it must not overlap earlier work of the same
+ * handle on another stream.  dci_b200_query_host uses the legacy default
+ * stream and synchronises it; that stream does not order against non-blocking
+ * streams.  Different handles are independent.
  */
 #ifndef DCI_B200_H
 #define DCI_B200_H
@@ -36,7 +46,7 @@ enum {
     DCI_B200_ERR_ARG = 1,        /* bad argument (message says which)          */
     DCI_B200_ERR_STATE = 2,      /* e.g. add() on a non-empty index            */
     DCI_B200_ERR_CUDA = 3,       /* a CUDA call failed                         */
-    DCI_B200_ERR_UNSUPPORTED = 4 /* e.g. blind querying                        */
+    DCI_B200_ERR_UNSUPPORTED = 4 /* e.g. a partition beyond the size limits    */
 };
 
 /* Message for the last non-zero status returned to this thread. */
@@ -97,8 +107,8 @@ int dci_b200_append(dci_b200_t *h, const float *d_all_data, int num_points_total
  * dci_query_config (include/dci.h:52-56) and stop each partition's traversal
  * exactly as the reference does (src/dci_cuda_kernel.cu:598-607).
  * block_size / thread_size must equal the values given to add (the reference
- * passes them on every call).  blind != 0 returns DCI_B200_ERR_UNSUPPORTED
- * (the reference's blind path writes out of bounds).
+ * passes them on every call).  blind != 0 returns DCI_B200_ERR_UNSUPPORTED:
+ * blind results have another length, see dci_b200_query_blind.
  * d_ids: [num_queries][num_neighbours] int32, d_dists: same shape fp32.  Slots
  * beyond the number of promoted points hold id -1 and distance +inf.
  * Any 1 <= num_neighbours <= num_points is accepted; above 1024 the selection
@@ -106,6 +116,15 @@ int dci_b200_append(dci_b200_t *h, const float *d_all_data, int num_points_total
 int dci_b200_query(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
                    int num_outer_iterations, int max_num_candidates, int blind,
                    int block_size, int thread_size, int *d_ids, float *d_dists, void *stream);
+
+/* dci_b200_query with the result in the form MDCI ships between GPUs (replaces the two float
+ * tensors that dciknn_cuda/core.py:146-151 moves per device): d_packed is
+ * [num_queries][num_neighbours] 64-bit keys, (fp32 bits of the distance << 32) | id, rows
+ * ascending, all ones in slots beyond the number of promoted points.  Input of
+ * dci_b200_merge_shards_packed. */
+int dci_b200_query_packed(dci_b200_t *h, const float *d_query, int num_queries, int num_neighbours,
+                          int num_outer_iterations, int max_num_candidates, int block_size,
+                          int thread_size, unsigned long long *d_packed, void *stream);
 
 /* A working form of the reference's blind querying, which its comments specify
  * (src/dci_cuda_kernel.cu:398-399, :775-776: no distance is computed, no
@@ -226,6 +245,12 @@ int dci_b200_last_projection_ms(dci_b200_t *h, float *h_ms);
 int dci_b200_merge_shards(const int *d_ids_in, const float *d_dists_in, int num_shards,
                           int num_queries, int k, const long long *id_offsets,
                           long long *d_ids_out, float *d_dists_out, int device, void *stream);
+
+/* The same merge for shard lists in dci_b200_query_packed's form: d_packed_in is
+ * [D][num_queries][k] keys with shard-local ids.  k up to 1024. */
+int dci_b200_merge_shards_packed(const unsigned long long *d_packed_in, int num_shards, int num_queries,
+                                 int k, const long long *id_offsets, long long *d_ids_out,
+                                 float *d_dists_out, int device, void *stream);
 
 /* Query for callers that must not allocate.  (No counterpart in the reference,
  * which allocates and frees managed and device memory inside every query,

@@ -32,6 +32,31 @@ class _OracleEngine:
         return torch.from_numpy(ids), torch.from_numpy(dists)
 
 
+class _PackedOracleEngine(_OracleEngine):
+    """The same stand-in with DCI.query_packed: one int64 key (distance bits << 32 | id) per slot."""
+
+    def query_packed(self, q, k, outer, max_num_candidates=None):
+        nq = q.shape[0]
+        out = np.full((nq, k), -1, np.int64)
+        n = self.o.num_points
+        if n > 0:
+            ids, dists = self.o.query(q.numpy(), min(k, n), outer, max_num_candidates)
+            key = (dists.view(np.uint32).astype(np.uint64) << np.uint64(32)) | ids.astype(np.uint32).astype(np.uint64)
+            key[ids < 0] = np.uint64(0xFFFFFFFFFFFFFFFF)
+            out[:, :ids.shape[1]] = key.view(np.int64)
+        return torch.from_numpy(out)
+
+
+def _host_merge_packed(packed, offsets, k):
+    key = packed.numpy().view(np.uint64)
+    empty = key == np.uint64(0xFFFFFFFFFFFFFFFF)
+    ids = (key & np.uint64(0xFFFFFFFF)).astype(np.int64)
+    dists = (key >> np.uint64(32)).astype(np.uint32).view(np.float32).copy()
+    ids[empty] = -1
+    dists[empty] = np.inf
+    return _host_merge(torch.from_numpy(ids), torch.from_numpy(dists), offsets, k)
+
+
 def _host_merge(ids, dists, offsets, k):
     ids = ids.numpy().astype(np.int64)
     for s, off in enumerate(offsets):
@@ -43,32 +68,35 @@ def _host_merge(ids, dists, offsets, k):
     return torch.from_numpy(np.take_along_axis(ids, order, 1)), torch.from_numpy(np.take_along_axis(d, order, 1))
 
 
-def _worker(rank, world, port, out_dir):
+def _worker(rank, world, port, out_dir, packed=False, n_points=1001):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     from dciknn_cuda_b200.core import MDCI, shard_bounds
     from tests import cases
     rng = np.random.default_rng(5)
-    data = cases.latent_linear(rng, 1001, 12, 24)
+    data = cases.latent_linear(rng, n_points, 12, 24)
     query = cases.latent_linear(rng, 17, 12, 24)
     projs = [cases.unit_rows(rng, 6, 24) for _ in range(world)]
-    eng = _OracleEngine(24, 2, 3, 7, 5, projs[rank])
-    m = MDCI(24, 2, 3, 7, 5, process_group=dist.group.WORLD, _local_engine=eng, _merge=_host_merge)
+    eng = (_PackedOracleEngine if packed else _OracleEngine)(24, 2, 3, 7, 5, projs[rank])
+    m = MDCI(24, 2, 3, 7, 5, process_group=dist.group.WORLD, _local_engine=eng, _merge=_host_merge,
+             _merge_packed=_host_merge_packed)
     m.add(torch.from_numpy(data))
-    dpd, bounds = shard_bounds(1001, world)
-    assert m.data_per_device == dpd == 1001 // world + 1 and eng.o.num_points == bounds[rank][1] - bounds[rank][0]
+    dpd, bounds = shard_bounds(n_points, world)
+    assert m.data_per_device == dpd == n_points // world + 1 and eng.o.num_points == bounds[rank][1] - bounds[rank][0]
     ids, dists = m.query(torch.from_numpy(query), 6, 200, max_num_candidates=30, return_int_ids=True)
     np.savez(os.path.join(out_dir, "rank%d.npz" % rank), ids=ids.numpy(), dists=dists.numpy())
     dist.barrier()
     dist.destroy_process_group()
 
 
-def test_two_gloo_ranks_match_reference_mdci_semantics(tmp_path):
+@pytest.mark.parametrize("packed", [False, True])
+def test_two_gloo_ranks_match_reference_mdci_semantics(tmp_path, packed):
+    """packed: the ranks exchange one tensor of 64-bit (distance, id) keys instead of two tensors."""
     from oracle import oracle
     from tests import cases
-    world, port = 2, 29500 + os.getpid() % 2000
-    mp.spawn(_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    world, port = 2, 29500 + (os.getpid() + 7 * packed) % 2000
+    mp.spawn(_worker, args=(world, port, str(tmp_path), packed), nprocs=world, join=True)
     rng = np.random.default_rng(5)
     data = cases.latent_linear(rng, 1001, 12, 24)
     query = cases.latent_linear(rng, 17, 12, 24)
@@ -79,6 +107,32 @@ def test_two_gloo_ranks_match_reference_mdci_semantics(tmp_path):
     for r in range(world):
         z = np.load(os.path.join(str(tmp_path), "rank%d.npz" % r))
         assert np.array_equal(z["ids"], oi) and np.array_equal(z["dists"], od)
+
+
+def test_trailing_empty_shard_contributes_nothing(tmp_path):
+    """6 points on 4 ranks: the reference's rule gives shards of 2, 2, 2 and 0 rows; the empty rank
+    still takes part in the gather and the merged lists are those of the three real shards."""
+    from oracle import oracle
+    from tests import cases
+    world, port = 4, 31500 + os.getpid() % 2000
+    mp.spawn(_worker, args=(world, port, str(tmp_path), True, 6), nprocs=world, join=True)
+    rng = np.random.default_rng(5)
+    data = cases.latent_linear(rng, 6, 12, 24)
+    query = cases.latent_linear(rng, 17, 12, 24)
+    projs = [cases.unit_rows(rng, 6, 24) for _ in range(world)]
+    want_i, want_d = [], []
+    for r in range(3):
+        o = oracle.OracleDCI(24, 2, 3, 7, 5, projs[r])
+        o.add(data[2 * r:2 * r + 2])
+        a, d = o.query(query, 2, 200, 30)
+        want_i.append(a.astype(np.int64) + 2 * r)
+        want_d.append(d)
+    want_i, want_d = np.concatenate(want_i, 1), np.concatenate(want_d, 1)
+    order = np.argsort(want_d, axis=1, kind="stable")
+    want_i, want_d = np.take_along_axis(want_i, order, 1), np.take_along_axis(want_d, order, 1)
+    for r in range(world):
+        z = np.load(os.path.join(str(tmp_path), "rank%d.npz" % r))
+        assert np.array_equal(z["ids"], want_i) and np.array_equal(z["dists"], want_d)
 
 
 def test_shard_bounds_follow_the_reference_rule():
