@@ -12,6 +12,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 #include <new>
 
@@ -43,17 +44,22 @@ int fail(int code, const char *fmt, ...) {
                         __LINE__, cudaGetErrorString(e_));                                 \
     } while (0)
 
+// every cudaMalloc / cudaFree this library issues goes through these two (dci_b200_device_alloc_calls)
+std::atomic<long long> g_alloc_calls{0};
+cudaError_t counted_malloc(void **p, size_t bytes) { ++g_alloc_calls; return cudaMalloc(p, bytes); }
+cudaError_t counted_free(void *p) { ++g_alloc_calls; return cudaFree(p); }
+
 struct Buf {
     void *p = nullptr;
     size_t cap = 0;
     cudaError_t ensure(size_t bytes) {
         if (bytes <= cap) return cudaSuccess;
-        if (p) { cudaFree(p); p = nullptr; cap = 0; }
-        cudaError_t e = cudaMalloc(&p, bytes);
+        if (p) { counted_free(p); p = nullptr; cap = 0; }
+        cudaError_t e = counted_malloc(&p, bytes);
         if (e == cudaSuccess) cap = bytes;
         return e;
     }
-    void release() { if (p) cudaFree(p); p = nullptr; cap = 0; }
+    void release() { if (p) counted_free(p); p = nullptr; cap = 0; }
 };
 
 struct DeviceGuard {
@@ -352,12 +358,12 @@ int dci_b200_create(dci_b200_t **out, int dim, int num_comp_indices, int num_sim
     h->sm_count = prop.multiProcessorCount;
     h->smem_optin = prop.sharedMemPerBlockOptin;
     h->smem_per_sm = prop.sharedMemPerMultiprocessor;
-    e = cudaMalloc((void **)&h->d_proj, sizeof(float) * (size_t)dim * h->L * h->S);
+    e = counted_malloc((void **)&h->d_proj, sizeof(float) * (size_t)dim * h->L * h->S);
     if (e != cudaSuccess) { delete h; return fail(DCI_B200_ERR_CUDA, "cudaMalloc(directions): %s", cudaGetErrorString(e)); }
     int rc = launch_directions(h, seed, 0);
     if (rc == 0 && (e = cudaDeviceSynchronize()) != cudaSuccess)
         rc = fail(DCI_B200_ERR_CUDA, "direction generation: %s", cudaGetErrorString(e));
-    if (rc) { cudaFree(h->d_proj); delete h; return rc; }
+    if (rc) { counted_free(h->d_proj); delete h; return rc; }
     *out = h;
     return 0;
 }
@@ -369,7 +375,7 @@ int dci_b200_destroy(dci_b200_t *h) {
     Buf *bufs[] = {&h->keys, &h->ids, &h->pos, &h->keysT, &h->tmp_keys, &h->qproj, &h->part_topk, &h->scratch, &h->merge_scratch, &h->stats, &h->phases, &h->errflag, &h->qbound,
                    &h->hq, &h->hids, &h->hdists};
     for (Buf *b : bufs) b->release();
-    if (h->d_proj) cudaFree(h->d_proj);
+    if (h->d_proj) counted_free(h->d_proj);
     for (auto &e : h->ev) if (e) cudaEventDestroy(e);
     for (auto &e : h->pev) if (e) cudaEventDestroy(e);
     delete h;
@@ -802,6 +808,8 @@ int dci_b200_get_phase_cycles(dci_b200_t *h, long long *h_out) {
 }
 
 long long dci_b200_launch_count(dci_b200_t *h) { return h ? h->launches : 0; }
+
+long long dci_b200_device_alloc_calls(void) { return g_alloc_calls.load(); }
 
 int dci_b200_set_projection(dci_b200_t *h, int mode) {
     if (int rc = check_handle(h)) return rc;

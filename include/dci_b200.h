@@ -205,6 +205,11 @@ int dci_b200_get_phase_cycles(dci_b200_t *h, long long *h_out);
 /* Number of kernels this library launched on behalf of this handle so far. */
 long long dci_b200_launch_count(dci_b200_t *h);
 
+/* Number of cudaMalloc and cudaFree calls this library has issued in this process, over all
+ * handles (every one of them goes through one counted wrapper).  Lets a caller, or a test, see
+ * that a call allocated nothing: the count is the same before and after. */
+long long dci_b200_device_alloc_calls(void);
+
 /* How data and queries are projected on the directions (replaces the
  * cublasSgemm calls of src/util_kernel.cu:45-80).  0 (default): exact fp32, one
  * fused multiply-add per term in ascending coordinate order -- the path every

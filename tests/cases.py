@@ -31,6 +31,44 @@ def c2_shaped(seed=1, n=40000, nq=24, P=4):
                 proj=unit_rows(rng, 20, 128))
 
 
+def mixture(rng, n, dim, centres=256):
+    """Rows around `centres` Gaussian centres (4 * randn), unit noise: the sharded 10M-point
+    configuration's distribution."""
+    c = (4.0 * rng.standard_normal((centres, dim))).astype(np.float32)
+    z = c[rng.integers(0, centres, n)] + rng.standard_normal((n, dim)).astype(np.float32)
+    return np.ascontiguousarray(z, dtype=np.float32)
+
+
+def unit_uniform(rng, n, dim):
+    """uniform[0, 1) entries, every row scaled to unit length: the high-dimensional configuration."""
+    z = rng.random((n, dim), dtype=np.float32)
+    return np.ascontiguousarray(z / np.linalg.norm(z, axis=1, keepdims=True), dtype=np.float32)
+
+
+def high_dim_shaped(seed=2, n=8000, nq=32, P=4):
+    """configs[2] cut down: dim 960 unit-length uniform rows, L=3, S=12 (36 simple indices), quota 10 000."""
+    rng = np.random.default_rng(seed)
+    z = unit_uniform(rng, n + nq, 960)
+    return dict(data=z[:n], query=z[n:], L=3, S=12, P=P, T=10, k=10, outer=5000, max_cand=10000,
+                proj=unit_rows(rng, 36, 960))
+
+
+def mixture_shaped(seed=3, n=40000, nq=96, P=4):
+    """configs[3] cut down: 256-centre Gaussian mixture in dim 96, L=2, S=10."""
+    rng = np.random.default_rng(seed)
+    z = mixture(rng, n + nq, 96)
+    return dict(data=z[:n], query=z[n:], L=2, S=10, P=P, T=10, k=10, outer=5000, max_cand=100,
+                proj=unit_rows(rng, 20, 96))
+
+
+def large_k_shaped(seed=4, n=4800, nq=8, P=4):
+    """configs[4] cut down: dim 256 from a 64-d latent, k=100, L=2, S=15, 20 000 outer iterations."""
+    rng = np.random.default_rng(seed)
+    z = latent_linear(rng, n + nq, 64, 256)
+    return dict(data=z[:n], query=z[n:], L=2, S=15, P=P, T=10, k=100, outer=20000, max_cand=1000,
+                proj=unit_rows(rng, 30, 256))
+
+
 EDGE_CASES = [
     # name,                N,    d, L, S, P,  T,  k, outer, max_cand, nq, special
     ("tiny_one_point",      1,    5, 1, 1, 1,  1,  1, 10,    10,       4, None),

@@ -50,6 +50,21 @@ def test_full_size_properties(full):
     assert hit >= 0.9, hit
 
 
+def test_full_size_answers_equal_the_oracle_bit_for_bit(full):
+    """The sequential restatement of the reference, run on the index the GPU built (1M points, 100
+    partitions of 10 000, 10 020 windows per composite index), must return the GPU's neighbours and
+    distance bits for the same queries."""
+    cfg, g, data_h, query_h, data = full
+    nq = 256
+    ids, dists = g.query(query_h[:nq].cuda(), cfg["k"], cfg["outer"], return_int_ids=True)
+    keys, sids = g.get_index()
+    qproj = oracle.project(g.get_proj().numpy(), query_h[:nq].numpy())
+    oi, od = oracle.query_index(keys.numpy(), sids.numpy(), cfg["L"], cfg["S"], cfg["P"], cfg["T"], data_h.numpy(),
+                                qproj, query_h[:nq].numpy(), cfg["k"], cfg["outer"], 10 * cfg["k"])
+    assert np.array_equal(ids.cpu().numpy(), oi)
+    assert np.array_equal(dists.cpu().numpy().view(np.uint32), od.view(np.uint32))
+
+
 def test_full_size_exhaustive_quota_gives_exact_knn(full):
     cfg, g, data_h, query_h, data = full
     q = query_h[:64].cuda()

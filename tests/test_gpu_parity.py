@@ -127,6 +127,18 @@ def test_c2_shaped_partitions():
     assert (os_[:, :, 5] == 0).all()          # the quota stops every partition before it runs out
 
 
+@pytest.mark.parametrize("shape", ["high_dim", "mixture", "large_k"])
+def test_shapes_of_the_other_benchmark_configurations(shape):
+    """Cut-down cases with the geometry and data distribution of the other configurations: dim 960 with
+    36 simple indices and a quota of 10 000; the 256-centre mixture in dim 96; k = 100 with S = 15 and
+    20 000 outer iterations.  Counters included."""
+    c = {"high_dim": lambda: cases.high_dim_shaped(n=6000, nq=12, P=3),
+         "mixture": lambda: cases.mixture_shaped(n=30000, nq=24, P=3),
+         "large_k": lambda: cases.large_k_shaped(n=4800, nq=8, P=4)}[shape]()
+    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
+    _assert_same(ids, dists, oi, od, gs, os_, shape, _limits(c))
+
+
 def test_large_partition_global_scratch_path():
     """One partition of 30 000 points does not fit shared memory: global-scratch variant."""
     rng = np.random.default_rng(3)
@@ -222,3 +234,45 @@ def test_mdci_two_shards_on_one_device_matches_oracle():
     assert np.array_equal(dists.cpu().numpy().view(np.uint32), od.view(np.uint32))
     f_ids, _ = m.query(torch.from_numpy(query).cuda(), 10)
     assert f_ids.dtype == torch.float32 and torch.equal(f_ids.long(), ids)
+
+
+def test_packed_lists_and_their_merge_equal_the_two_tensor_path():
+    """dci_b200_query_packed + dci_b200_merge_shards_packed (what MDCI ships between GPUs) against
+    dci_b200_query + dci_b200_merge_shards, including a shard shorter than k."""
+    from dciknn_cuda_b200 import DCI
+    from dciknn_cuda_b200.core import merge_shards, merge_shards_packed
+    rng = np.random.default_rng(12)
+    query = torch.from_numpy(cases.latent_linear(rng, 21, 10, 32)).cuda()
+    sizes, k = (2500, 1800, 4), 7
+    packed, ids, dists = [], [], []
+    for n in sizes:
+        g = DCI(32, 2, 4, 6, 10, 0, seed=100 + n)
+        g.add(torch.from_numpy(cases.latent_linear(rng, n, 10, 32)).cuda())
+        p = g.query_packed(query, k)
+        assert p.shape == (21, k) and p.dtype == torch.int64
+        a = torch.full((21, k), -1, dtype=torch.int32, device="cuda")
+        d = torch.full((21, k), float("inf"), device="cuda")
+        ai, di = g.query(query, min(k, n), return_int_ids=True)
+        a[:, :ai.shape[1]], d[:, :di.shape[1]] = ai, di
+        assert torch.equal(p >> 32, torch.where(a >= 0, d.view(torch.int32).long(), torch.full_like(p, -1)))
+        assert torch.equal(p & 0xFFFFFFFF, torch.where(a >= 0, a.long(), torch.full_like(p, 0xFFFFFFFF)))
+        packed.append(p); ids.append(a); dists.append(d)
+    offsets = [0, 2501, 5002]
+    want = merge_shards(torch.stack(ids).contiguous(), torch.stack(dists).contiguous(), offsets, k)
+    got = merge_shards_packed(torch.stack(packed).contiguous(), offsets, k)
+    assert torch.equal(got[0], want[0]) and torch.equal(got[1].view(torch.int32), want[1].view(torch.int32))
+
+
+def test_mdci_with_an_empty_trailing_shard():
+    """9 points on 4 shards: the reference's rule leaves the last shard without rows."""
+    from dciknn_cuda_b200 import MDCI
+    rng = np.random.default_rng(13)
+    data = cases.latent_linear(rng, 9, 4, 8)
+    query = cases.latent_linear(rng, 5, 4, 8)
+    m = MDCI(8, 1, 2, 2, 3, devices=[0, 0, 0, 0], seeds=[1, 2, 3, 4])
+    m.add(torch.from_numpy(data))
+    assert [g.num_points for g in m.dcis] == [3, 3, 3, 0]
+    ids, dists = m.query(torch.from_numpy(query).cuda(), 9, max_num_candidates=1000, return_int_ids=True)
+    bi, bd = oracle.bruteforce(data, query, 9)          # every point is retrieved: exact k-NN of all 9
+    assert np.array_equal(dists.cpu().numpy().view(np.uint32), bd.view(np.uint32))
+    assert np.array_equal(np.sort(ids.cpu().numpy(), 1), np.sort(bi, 1))

@@ -41,6 +41,15 @@ def test_invalid_index_is_rejected():
     bad[0, 10], bad[0, 11] = keys[0, 11] + 1.0, keys[0, 10] - 1.0      # not ascending any more
     with pytest.raises(ValueError):
         g.set_index(data, bad, ids)
+    # a point named twice (and so another one never): ids stay inside the partition and keys stay
+    # ascending, yet the segment is not a permutation and the point left out would have no position
+    dup = ids.clone()
+    dup[1, 7] = dup[1, 8]
+    with pytest.raises(ValueError, match="twice"):
+        g.set_index(data, keys, dup)
+    assert g.num_points == 0
+    with pytest.raises(RuntimeError):       # nothing is launched on a rejected index
+        g.query(data[:2], 3)
     g.set_index(data, keys, ids)
     assert g.num_points == 500
 

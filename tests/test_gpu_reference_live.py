@@ -37,12 +37,12 @@ def _compare(c, nq_ref):
         else:
             ref.set_proj(proj)
         ref.add(data)
-        ids, dists = ref.query(query, c["k"], c["outer"])
+        ids, dists = ref.query(query, c["k"], c["outer"], c.get("max_cand"))
         out[tag] = (ids.cpu().numpy(), dists.cpu().numpy())
         ref.free()
     g = DCI(dim, c["L"], c["S"], c["P"], c["T"], 0, proj=torch.from_numpy(proj))
     g.add(data)
-    ids, dists = g.query(query, c["k"], c["outer"], return_int_ids=True)
+    ids, dists = g.query(query, c["k"], c["outer"], max_num_candidates=c.get("max_cand"), return_int_ids=True)
     ids, dists = ids.cpu().numpy(), dists.cpu().numpy()
     fi, fd = out["fixed"]
     ai, ad = out["asis"]
@@ -66,3 +66,30 @@ def test_example_configuration_against_reference_build():
 def test_c2_shaped_against_reference_build():
     c = cases.c2_shaped(n=40000, nq=192, P=4)   # partitions of 10 000 points as in configs[1]
     _compare(c, 192)
+
+
+def test_high_dim_shape_against_reference_build():
+    """dim 960, unit-length uniform rows, L=3 x S=12 = 36 simple indices, quota 10 000 passed straight
+    to the reference's dci_query (its Python layer cannot set it): exhaustive partitions."""
+    c = cases.high_dim_shaped(n=8000, nq=32, P=4)
+    _compare(c, 32)
+
+
+def test_mixture_shape_against_reference_build():
+    """The sharded configuration's data: 256 Gaussian centres in dim 96, partitions of 10 000 points."""
+    c = cases.mixture_shaped(n=40000, nq=96, P=4)
+    _compare(c, 96)
+
+
+def test_one_large_partition_against_reference_build():
+    """One partition of 70 001 points of the mixture: 32-bit positions and the variant that keeps its
+    work arrays in global memory meet the reference's own build."""
+    c = cases.mixture_shaped(seed=5, n=70001, nq=6, P=1)
+    _compare(c, 6)
+
+
+def test_large_k_shape_against_reference_build():
+    """k = 100 with S = 15 and 20 000 outer iterations, dim 256 from a 64-d latent: lane 0 cannot reach
+    its quota of 1 000 in partitions of 1 200 points, so every point is retrieved."""
+    c = cases.large_k_shaped(n=4800, nq=8, P=4)
+    _compare(c, 8)

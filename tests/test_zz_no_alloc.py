@@ -46,16 +46,56 @@ def test_noalloc_query_matches_regular_query_twice():
     assert torch.equal(ids, want_ids) and torch.equal(dists.view(torch.int32), want_dists.view(torch.int32))
 
 
+def _alloc_calls():
+    from dciknn_cuda_b200 import _capi
+    return int(_capi.lib().dci_b200_device_alloc_calls())
+
+
+def test_noalloc_query_allocates_nothing_even_on_its_first_call_with_tensor_core_projection():
+    """With the tcgen05 projection selected the regular path keeps a flag word for the kernel's
+    bounded waits in a buffer it creates on first use, and creates timing events when timing is on;
+    the allocation-free call takes the word from the fixed array and records no timing.  The handle
+    below has never projected anything when its first allocation-free call runs, and the library's
+    count of cudaMalloc/cudaFree calls must not move across that call or the next."""
+    from dciknn_cuda_b200 import DCI
+    c = cases.c2_shaped(n=20000, nq=64, P=2)
+    data = torch.from_numpy(c["data"]).cuda()
+    q = torch.from_numpy(c["query"]).cuda()
+    ref = DCI(128, c["L"], c["S"], c["P"], c["T"], 0, proj=torch.from_numpy(c["proj"]))
+    ref.set_projection("tf32x3")
+    ref.add(data)
+    want_ids, want_dists = ref.query(q, c["k"], c["outer"], return_int_ids=True)
+    # a second handle whose index is installed, not projected: its first projection is the call below
+    g = DCI(128, c["L"], c["S"], c["P"], c["T"], 0, proj=torch.from_numpy(c["proj"]))
+    g.set_projection("tf32x3")
+    keys, ids_idx = ref.get_index()
+    g.set_index(data, keys, ids_idx)
+    g.enable_timing(True)                                   # the regular path would create events
+    ids, dists = torch.empty_like(want_ids), torch.empty_like(want_dists)
+    torch.cuda.synchronize()
+    before = _alloc_calls()
+    free_before = torch.cuda.mem_get_info()[0]
+    for _ in range(2):
+        g.query_noalloc(q, ids, dists, c["outer"])
+        torch.cuda.synchronize()
+        assert _alloc_calls() == before
+        assert torch.equal(ids, want_ids) and torch.equal(dists.view(torch.int32), want_dists.view(torch.int32))
+    assert torch.cuda.mem_get_info()[0] == free_before
+
+
 def test_noalloc_query_on_other_geometries_and_after_other_work():
-    for row in (cases.EDGE_CASES[2], cases.EDGE_CASES[6], cases.EDGE_CASES[14]):
+    # ragged partitions (64-thread CTAs), 36 indices, k = 700, rows that are not 32-byte aligned (dim 37)
+    for row in (cases.EDGE_CASES[2], cases.EDGE_CASES[6], cases.EDGE_CASES[7], cases.EDGE_CASES[14]):
         c = cases.edge_case(row)
         g = _make(c)
         q = torch.from_numpy(c["query"]).cuda()
         want_ids, want_dists = g.query(q, c["k"], c["outer"], max_num_candidates=c["max_cand"], return_int_ids=True)
         ids, dists = torch.empty_like(want_ids), torch.empty_like(want_dists)
+        before = _alloc_calls()
         for _ in range(2):
             g.query_noalloc(q, ids, dists, c["outer"], max_num_candidates=c["max_cand"])
             torch.cuda.synchronize()
+            assert _alloc_calls() == before, c["name"]
             assert torch.equal(ids, want_ids), c["name"]
             assert torch.equal(dists.view(torch.int32), want_dists.view(torch.int32)), c["name"]
 
