@@ -75,34 +75,38 @@ WORKLOAD_LABEL = {"configs1": "configs[1]", "configs2": "configs[2]", "configs3_
                   "configs4_shard": "configs[4] (one of 8 shards)"}
 
 
-def make_data(seed, n, nq, cfg):
+def make_data(seed, n, nq, cfg, stream=0):
     """Seeded synthetic rows; the last nq rows are the queries.  Default kind: randn(., latent) @
-    randn(latent, dim) + noise * randn."""
+    randn(latent, dim) + noise * randn.  `stream` > 0 draws other rows of the SAME distribution
+    (same linear map, same centres): the shards of ranks above 0."""
     g = torch.Generator().manual_seed(seed)
+    rows = g if stream == 0 else torch.Generator().manual_seed(seed + 1000 * stream)
     kind = cfg.get("kind", "latent")
     if kind == "unit_uniform":
-        z = torch.rand(n + nq, cfg["dim"], generator=g)
+        z = torch.rand(n + nq, cfg["dim"], generator=rows)
         z /= z.norm(dim=1, keepdim=True)
     elif kind == "mixture":
         centres = 4.0 * torch.randn(256, cfg["dim"], generator=g)
-        z = centres[torch.randint(256, (n + nq,), generator=g)] + torch.randn(n + nq, cfg["dim"], generator=g)
+        z = centres[torch.randint(256, (n + nq,), generator=rows)] + torch.randn(n + nq, cfg["dim"], generator=rows)
     else:
         a = torch.randn(cfg["latent"], cfg["dim"], generator=g)
-        z = torch.randn(n + nq, cfg["latent"], generator=g) @ a
+        z = torch.randn(n + nq, cfg["latent"], generator=rows) @ a
         if cfg.get("noise"):
-            z += cfg["noise"] * torch.randn(n + nq, cfg["dim"], generator=g)
+            z += cfg["noise"] * torch.randn(n + nq, cfg["dim"], generator=rows)
     return z[:n].contiguous(), z[n:].contiguous()
 
 
 MIX_BLOCK = 1 << 16
 
 
-def mixture_rows(seed, lo, hi, dim):
+def mixture_rows(seed, lo, hi, dim, stream=0):
     """Rows [lo, hi) of a seeded 256-centre Gaussian mixture whose rows are drawn block by block
     (block j of 65 536 rows has its own generator), so that a rank can draw its shard of a large
-    set without drawing the rest, and every rank count cuts the SAME point set."""
+    set without drawing the rest, and every rank count cuts the SAME point set.  `stream` selects an
+    independent row sequence around the same centres (the queries)."""
     g = torch.Generator().manual_seed(seed)
     centres = 4.0 * torch.randn(256, dim, generator=g)
+    seed = seed + 7919 * stream
     out = torch.empty(hi - lo, dim)
     for j in range(lo // MIX_BLOCK, (hi + MIX_BLOCK - 1) // MIX_BLOCK):
         gb = torch.Generator().manual_seed(seed * 1_000_003 + 17 + j)
@@ -349,7 +353,7 @@ def sharded_10m(R, args):
     dpd, bounds = shard_bounds(N, R.world)
     lo, hi = bounds[R.rank]
     shard = mixture_rows(3, lo, hi, cfg["dim"]).to(R.dev)
-    query_h = mixture_rows(4003, 0, nq, cfg["dim"])
+    query_h = mixture_rows(3, 0, nq, cfg["dim"], stream=1)
     query = query_h.to(R.dev)
     if R.world == 1:
         engine = DCI(cfg["dim"], cfg["L"], cfg["S"], cfg["P"], cfg["T"], R.local, seed=3030)
@@ -408,10 +412,10 @@ def bench_ours(args):
     if args.queries:
         cfg["n_queries"] = args.queries
     mc = cfg.get("max_cand")
-    # every rank draws the same queries (seed 1); rank r > 0 draws its own shard
+    # every rank draws the same queries (seed 1); rank r > 0 draws its own shard of the same distribution
     data_h, query_h = make_data(1, cfg["n_points"], cfg["n_queries"], cfg)
     if rank > 0:
-        data_h, _ = make_data(1 + 1000 * rank, cfg["n_points"], 0, cfg)
+        data_h, _ = make_data(1, cfg["n_points"], 0, cfg, stream=rank)
     data = data_h.to(dev)
     query = query_h.to(dev)
     dpd = cfg["n_points"] + 1
@@ -652,7 +656,7 @@ def bench_reference(args):
     dev = R.dev
     data_h, query_h = make_data(1, cfg["n_points"], cfg["n_queries"], cfg)
     if rank > 0:
-        data_h, _ = make_data(1 + 1000 * rank, cfg["n_points"], 0, cfg)
+        data_h, _ = make_data(1, cfg["n_points"], 0, cfg, stream=rank)
     data, query = data_h.to(dev), query_h.to(dev)
     dpd = cfg["n_points"] + 1
     k = cfg["k"]
