@@ -49,6 +49,16 @@ SYMBOLS = [
     ("dci_b200_merge_shards", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, _c_llp, _vp, _vp, C.c_int, _vp]),
     ("dci_b200_query_packed", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp]),
     ("dci_b200_merge_shards_packed", C.c_int, [_vp, C.c_int, C.c_int, C.c_int, _c_llp, _vp, _vp, C.c_int, _vp]),
+    ("dci_b200_mdci_create", C.c_int, [C.POINTER(_vp), C.c_int, C.c_int, C.c_int, _c_ip, C.c_int,
+                                       C.POINTER(C.c_ulonglong)]),
+    ("dci_b200_mdci_destroy", C.c_int, [_vp]),
+    ("dci_b200_mdci_num_devices", C.c_int, [_vp]),
+    ("dci_b200_mdci_shard", _vp, [_vp, C.c_int]),
+    ("dci_b200_mdci_data_per_device", C.c_longlong, [_vp]),
+    ("dci_b200_mdci_add", C.c_int, [_vp, _vp, C.c_longlong, C.c_int, C.c_int]),
+    ("dci_b200_mdci_clear", C.c_int, [_vp]),
+    ("dci_b200_mdci_query", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp, _vp]),
+    ("dci_b200_mdci_query_host", C.c_int, [_vp, _vp, C.c_int, C.c_int, C.c_int, C.c_int, _vp, _vp]),
 ]
 
 ERR_ARG, ERR_STATE, ERR_CUDA, ERR_UNSUPPORTED = 1, 2, 3, 4

@@ -59,6 +59,7 @@ build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_in
         const int n = (int)min((long long)ppb, (long long)N - lo);
         const size_t row = segment_start(lo, i, num_indices, n);
         const size_t urow = (size_t)i * N + lo;               // the projection writes [I][N]
+        const size_t prow = pos_segment_start(b, i, num_indices, ppb);
         for (int x = threadIdx.x; x < n; x += blockDim.x) {
             kA[x] = float_to_ordered(keys_unsorted[urow + x]);
             vA[x] = (ValT)x;
@@ -71,8 +72,9 @@ build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_in
             skeysT[row + r * qn + min(r, rem) + j] = ordered_to_float(kA[x]);
             skeys[row + x] = ordered_to_float(kA[x]);
             sids[row + x] = (int)(lo + vA[x]);
-            spos[row + vA[x]] = (ValT)x;
+            spos[prow + vA[x]] = (ValT)x;
         }
+        for (int x = n + threadIdx.x; x < pos_stride(ppb); x += blockDim.x) spos[prow + x] = (ValT)0;
         __syncthreads();
     }
 }
@@ -93,6 +95,7 @@ __global__ void derive_index_kernel(const float *__restrict__ in_keys, const int
         const int n = (int)min((long long)ppb, (long long)N - lo);
         const size_t row = segment_start(lo, i, num_indices, n);
         const size_t urow = (size_t)i * N + lo;
+        const size_t prow = pos_segment_start(b, i, num_indices, ppb);
         const int qn = n / T, rem = n % T;
         for (int x = threadIdx.x; x < n; x += blockDim.x) {
             const long long p = (long long)in_ids[urow + x] - lo;
@@ -103,7 +106,7 @@ __global__ void derive_index_kernel(const float *__restrict__ in_keys, const int
             }
             skeys[row + x] = key;
             sids[row + x] = in_ids[urow + x];
-            spos[row + p] = (PosT)x;
+            spos[prow + p] = (PosT)x;
             const int r = x % T, j = x / T;
             skeysT[row + r * qn + min(r, rem) + j] = key;
         }
@@ -113,9 +116,10 @@ __global__ void derive_index_kernel(const float *__restrict__ in_keys, const int
 // Second half of the validation of an installed index: every point of a partition must occur exactly
 // once in each of its segments.  The caller fills spos with 0xFF bytes before derive_index_kernel, so
 // a point that no entry named still holds the sentinel (>= n), and a point named twice leaves another
-// one unnamed.  Sets *bad otherwise.  Same segment loop as derive_index_kernel.
+// one unnamed.  Sets *bad otherwise, and zeroes the padding behind each segment's positions.  Same
+// segment loop as derive_index_kernel.
 template <typename PosT>
-__global__ void check_index_kernel(const int *__restrict__ sids, const PosT *__restrict__ spos, int N,
+__global__ void check_index_kernel(const int *__restrict__ sids, PosT *__restrict__ spos, int N,
                                    int num_indices, int ppb, int num_parts, int *bad) {
     const long long nseg = (long long)num_indices * num_parts;
     for (long long seg = blockIdx.x; seg < nseg; seg += gridDim.x) {
@@ -123,10 +127,12 @@ __global__ void check_index_kernel(const int *__restrict__ sids, const PosT *__r
         const long long lo = (long long)b * ppb;
         const int n = (int)min((long long)ppb, (long long)N - lo);
         const size_t row = segment_start(lo, i, num_indices, n);
+        const size_t prow = pos_segment_start(b, i, num_indices, ppb);
         for (int p = threadIdx.x; p < n; p += blockDim.x) {
-            const long long x = (long long)spos[row + p];
+            const long long x = (long long)spos[prow + p];
             if (x >= n || (long long)sids[row + x] != lo + p) atomicExch(bad, 1);
         }
+        for (int p = n + threadIdx.x; p < pos_stride(ppb); p += blockDim.x) spos[prow + p] = (PosT)0;
     }
 }
 

@@ -232,49 +232,52 @@ __device__ void cta_radix_sort(uint32_t *kA, ValT *vA, uint32_t *kB, ValT *vB, i
 
 constexpr int kMaxBucket = 48;   // largest bucket the counting rank accepts
 
-// Bucket of a non-negative fp32 key: equal-width value buckets, a monotone map.
+// Bucket of a non-negative fp32 key: equal-width value buckets, a monotone map.  key * scale is
+// rounded to an integer by adding 2^23 (the sum's low mantissa bits are then that integer): one
+// fused multiply-add and one subtraction instead of a float-to-int conversion, which runs at a
+// fraction of the rate.  Needs key * scale < 2^22; the number of buckets is far below that.
 __device__ __forceinline__ int bucket_of(uint32_t key_bits, float scale, int last) {
-    return min(last, (int)(__uint_as_float(key_bits) * scale));
+    return min(last, __float_as_int(__fmaf_rn(__uint_as_float(key_bits), scale, 8388608.0f)) - 0x4B000000);
 }
 
 // Second half of the counting rank.  Precondition: every key w in [0, W) has
 // been dropped into bucket_of(key[w]) with slot[w] = its arrival number there
 // and cnt[b] = the size of bucket b (all <= kMaxBucket), cnt[nbuckets] = 0.
-// Lists the key indices bucket by bucket in bval, then gives every key its rank
-// in ascending (key, tie order): rank = start of its bucket + number of smaller
-// keys inside the bucket.  tie_less(a, b) orders two key indices whose keys are
-// equal.  rank_out[w] receives the rank.  Ends with a barrier.
+// Lists the keys bucket by bucket (bkey: the key, bval: its index), then gives
+// every key its rank in ascending (key, tie order): rank = start of its bucket
+// + number of smaller keys inside the bucket.  The ranking walks the bucket
+// ordered lists, so a warp reads consecutive entries, its counter reads fall on
+// the same or neighbouring words and the bucket mates it compares with lie next
+// to its own entry: the only scattered access left is the store of the rank.
+// tie_less(a, b) orders two key indices whose keys are equal.  rank_out[w]
+// receives the rank.  Ends with a barrier.
 template <typename ValT, typename CntT, typename TieLess, typename Mark>
 __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, int W, const uint8_t *slot,
-                                                          ValT *bval, CntT *cnt, int nbuckets, float scale,
-                                                          uint32_t *scratch, ValT *rank_out, TieLess tie_less,
-                                                          Mark mark) {
+                                                          ValT *bval, uint32_t *bkey, CntT *cnt, int nbuckets,
+                                                          float scale, uint32_t *scratch, ValT *rank_out,
+                                                          TieLess tie_less, Mark mark) {
     const int tid = threadIdx.x, last = nbuckets - 1;
     cta_scan_counters(cnt, nbuckets + 1, scratch);           // cnt[b] = start of bucket b, cnt[nbuckets] = W
     mark(8);
-    for (int w = tid; w < W; w += blockDim.x)
-        bval[(uint32_t)cnt[bucket_of(key[w], scale, last)] + (uint32_t)slot[w]] = (ValT)w;
-    __syncthreads();
-    mark(9);
     for (int w = tid; w < W; w += blockDim.x) {
         const uint32_t k = key[w];
+        const uint32_t dest = (uint32_t)cnt[bucket_of(k, scale, last)] + (uint32_t)slot[w];
+        bval[dest] = (ValT)w;
+        bkey[dest] = k;
+    }
+    __syncthreads();
+    mark(9);
+    for (int j = tid; j < W; j += blockDim.x) {
+        const uint32_t k = bkey[j];
         const int b = bucket_of(k, scale, last);
         const uint32_t lo = cnt[b], hi = cnt[b + 1];
         uint32_t r = lo;
-        if (hi - lo > 1)                                 // alone in its bucket: the rank is the bucket start
-        for (uint32_t j0 = lo; j0 < hi; j0 += 4) {      // four bucket mates at a time: independent loads
-            uint32_t other[4], kj[4];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) other[u] = j0 + u < hi ? (uint32_t)bval[j0 + u] : (uint32_t)w;
-#pragma unroll
-            for (int u = 0; u < 4; ++u) kj[u] = key[other[u]];
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (kj[u] < k) ++r;
-                else if (kj[u] == k && other[u] != (uint32_t)w && tie_less(other[u], (uint32_t)w)) ++r;
-            }
+        for (uint32_t j2 = lo; j2 < hi; ++j2) {
+            const uint32_t k2 = bkey[j2];
+            if (k2 < k) ++r;
+            else if (k2 == k && j2 != (uint32_t)j && tie_less((uint32_t)bval[j2], (uint32_t)bval[j])) ++r;
         }
-        rank_out[w] = (ValT)r;
+        rank_out[bval[j]] = (ValT)r;
     }
     __syncthreads();
 }
@@ -470,6 +473,15 @@ __device__ __forceinline__ void topk_slot_close(TopKSlot *s, const CtaTopK &t, c
 // partition), I simple indices in all.
 __host__ __device__ __forceinline__ size_t segment_start(long long lo, int i, int I, int n) {
     return (size_t)lo * (size_t)I + (size_t)i * (size_t)n;
+}
+
+// The inverse permutation (position of each point in its sorted segment) has a layout of its own:
+// every segment starts on a multiple of 8 entries, segment (partition b, simple index i) at
+// (b * I + i) * pos_stride(ppb), so that the positions of neighbouring points can be read with
+// aligned vector loads.  The entries between a segment's n points and the stride are zero.
+__host__ __device__ __forceinline__ int pos_stride(int ppb) { return (ppb + 7) & ~7; }
+__host__ __device__ __forceinline__ size_t pos_segment_start(long long b, int i, int I, int ppb) {
+    return ((size_t)b * (size_t)I + (size_t)i) * (size_t)pos_stride(ppb);
 }
 
 }  // namespace dci

@@ -413,11 +413,16 @@ static int check_partition_limits(dci_b200 *h, int ppb, int thread_size) {
     return 0;
 }
 
-static int ensure_index_buffers(dci_b200 *h, size_t n_entries, int ppb) {
+// bytes of the position array: every (partition, simple index) segment padded to pos_stride(ppb)
+static size_t pos_bytes(int I, int num_parts, int ppb) {
+    return (size_t)I * num_parts * dci::pos_stride(ppb) * (ppb <= 65535 ? sizeof(uint16_t) : sizeof(uint32_t));
+}
+
+static int ensure_index_buffers(dci_b200 *h, size_t n_entries, int ppb, int num_parts) {
     DCI_CUDA(h->keys.ensure(n_entries * sizeof(float)));
     DCI_CUDA(h->ids.ensure(n_entries * sizeof(int)));
     DCI_CUDA(h->keysT.ensure(n_entries * sizeof(float)));
-    DCI_CUDA(h->pos.ensure(n_entries * (ppb <= 65535 ? sizeof(uint16_t) : sizeof(uint32_t))));
+    DCI_CUDA(h->pos.ensure(pos_bytes(h->L * h->S, num_parts, ppb)));
     return 0;
 }
 
@@ -437,7 +442,7 @@ int dci_b200_add(dci_b200_t *h, const float *d_data, int num_points, int block_s
     const int num_parts = (num_points + ppb - 1) / ppb;
     if (int rc = check_partition_limits(h, ppb, thread_size)) return rc;
     const size_t n_entries = (size_t)I * num_points;
-    if (int rc = ensure_index_buffers(h, n_entries, ppb)) return rc;
+    if (int rc = ensure_index_buffers(h, n_entries, ppb, num_parts)) return rc;
     DCI_CUDA(h->tmp_keys.ensure(n_entries * sizeof(float)));
     h->num_points = num_points; h->P = block_size; h->T = thread_size; h->ppb = ppb; h->num_parts = num_parts;
     h->d_data = d_data;
@@ -490,7 +495,7 @@ int dci_b200_append(dci_b200_t *h, const float *d_all_data, int num_points_total
     DCI_CUDA_OR_EMPTY(cudaStreamSynchronize(st));
 #undef DCI_CUDA_OR_EMPTY
     // 3. every segment again, for the partition bounds of the new point count
-    if (int rc = ensure_index_buffers(h, (size_t)I * n_new, ppb)) { h->num_points = 0; h->d_data = nullptr; return rc; }
+    if (int rc = ensure_index_buffers(h, (size_t)I * n_new, ppb, num_parts)) { h->num_points = 0; h->d_data = nullptr; return rc; }
     h->num_points = n_new; h->ppb = ppb; h->num_parts = num_parts; h->d_data = d_all_data;
     int rc = (ppb <= 65535) ? launch_build<uint16_t>(h, (const float *)h->tmp_keys.p, st)
                             : launch_build<uint32_t>(h, (const float *)h->tmp_keys.p, st);
@@ -523,7 +528,7 @@ int dci_b200_set_index(dci_b200_t *h, const float *d_data, int num_points, int b
     DCI_CUDA(h->keys.ensure(n_entries * sizeof(float)));
     DCI_CUDA(h->ids.ensure(n_entries * sizeof(int)));
     DCI_CUDA(h->keysT.ensure(n_entries * sizeof(float)));
-    DCI_CUDA(h->pos.ensure(n_entries * (ppb <= 65535 ? sizeof(uint16_t) : sizeof(uint32_t))));
+    DCI_CUDA(h->pos.ensure(pos_bytes(I, num_parts, ppb)));
     DCI_CUDA(h->errflag.ensure(sizeof(int)));
     DCI_CUDA(cudaMemsetAsync(h->errflag.p, 0, sizeof(int), st));
     // the caller's arrays are [I][N]; the kernel checks them and writes the partition-major index
@@ -534,18 +539,18 @@ int dci_b200_set_index(dci_b200_t *h, const float *d_data, int num_points, int b
     const unsigned grid = (unsigned)std::min<long long>((long long)I * num_parts, (long long)h->sm_count * 8);
     // positions start as a sentinel (all ones, beyond any partition) so that the second kernel sees
     // every point that no entry of its segment names
-    DCI_CUDA(cudaMemsetAsync(h->pos.p, 0xFF, n_entries * (ppb <= 65535 ? sizeof(uint16_t) : sizeof(uint32_t)), st));
+    DCI_CUDA(cudaMemsetAsync(h->pos.p, 0xFF, pos_bytes(I, num_parts, ppb), st));
     if (ppb <= 65535) {
         dci::derive_index_kernel<uint16_t><<<grid, 256, 0, st>>>(
             (const float *)h->tmp_keys.p, (const int *)h->scratch.p, num_points, I, ppb, num_parts, thread_size,
             (float *)h->keys.p, (int *)h->ids.p, (uint16_t *)h->pos.p, (float *)h->keysT.p, (int *)h->errflag.p);
-        dci::check_index_kernel<uint16_t><<<grid, 256, 0, st>>>((const int *)h->ids.p, (const uint16_t *)h->pos.p,
+        dci::check_index_kernel<uint16_t><<<grid, 256, 0, st>>>((const int *)h->ids.p, (uint16_t *)h->pos.p,
                                                                num_points, I, ppb, num_parts, (int *)h->errflag.p);
     } else {
         dci::derive_index_kernel<uint32_t><<<grid, 256, 0, st>>>(
             (const float *)h->tmp_keys.p, (const int *)h->scratch.p, num_points, I, ppb, num_parts, thread_size,
             (float *)h->keys.p, (int *)h->ids.p, (uint32_t *)h->pos.p, (float *)h->keysT.p, (int *)h->errflag.p);
-        dci::check_index_kernel<uint32_t><<<grid, 256, 0, st>>>((const int *)h->ids.p, (const uint32_t *)h->pos.p,
+        dci::check_index_kernel<uint32_t><<<grid, 256, 0, st>>>((const int *)h->ids.p, (uint32_t *)h->pos.p,
                                                                num_points, I, ppb, num_parts, (int *)h->errflag.p);
     }
     h->launches += 2;
@@ -897,6 +902,230 @@ int dci_b200_merge_shards_packed(const unsigned long long *d_packed_in, int num_
         reinterpret_cast<const uint64_t *>(d_packed_in), num_shards, num_queries, k, cap, off, d_ids_out, d_dists_out);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(DCI_B200_ERR_CUDA, "merge_shards_packed launch: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------
+// MDCI below Python: the reference shards one point set over several devices and runs the
+// per-device queries from host threads (dciknn_cuda/core.py:110-157, src/dci_cuda.cpp:120-134).
+// Here one host thread drives every device: all calls of this library are asynchronous, so the D
+// shards are projected, sorted and queried side by side on their own streams; the queries reach the
+// other devices and the packed lists come back to devices[0] as peer copies over NVLink, ordered
+// with events, and devices[0] merges.
+struct dci_b200_mdci {
+    int D = 0, dim = 0, P = 0, T = 0;
+    long long num_points = 0, dpd = 0;
+    int dev[64];
+    dci_b200 *shard[64];
+    cudaStream_t st[64];
+    cudaEvent_t ev[64];
+    cudaEvent_t ev_query = nullptr;
+    Buf data[64], query[64], lists[64], tmp[64];   // per device: owned shard rows, query copy, packed lists, short lists
+    Buf gathered, q0, ids0, dists0;                 // on dev[0]
+};
+
+namespace {
+
+int mdci_check(dci_b200_mdci *m) {
+    if (!m) return fail(DCI_B200_ERR_ARG, "null MDCI handle");
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int dci_b200_mdci_create(dci_b200_mdci_t **out, int dim, int num_comp_indices, int num_simp_indices,
+                         const int *devices, int num_devices, const unsigned long long *seeds) {
+    if (!out) return fail(DCI_B200_ERR_ARG, "out is null");
+    *out = nullptr;
+    if (!devices || num_devices < 1 || num_devices > 64)
+        return fail(DCI_B200_ERR_ARG, "MDCI needs 1 to 64 devices, got %d", num_devices);
+    dci_b200_mdci *m = new (std::nothrow) dci_b200_mdci();
+    if (!m) return fail(DCI_B200_ERR_CUDA, "host allocation failed");
+    m->dim = dim;
+    for (int i = 0; i < 64; ++i) { m->shard[i] = nullptr; m->st[i] = nullptr; m->ev[i] = nullptr; m->dev[i] = 0; }
+    int rc = 0;
+    for (int i = 0; i < num_devices && !rc; ++i) {
+        m->dev[i] = devices[i];
+        // every shard has its own directions, as in the reference (one _dci_new per device, core.py:117)
+        rc = dci_b200_create(&m->shard[i], dim, num_comp_indices, num_simp_indices, devices[i],
+                             seeds ? seeds[i] : 0x9E3779B97F4A7C15ull * (unsigned long long)(i + 1));
+        if (rc) break;
+        m->D = i + 1;
+        DeviceGuard g(devices[i]);
+        if (cudaStreamCreateWithFlags(&m->st[i], cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&m->ev[i], cudaEventDisableTiming) != cudaSuccess)
+            rc = fail(DCI_B200_ERR_CUDA, "cannot create a stream or an event on device %d", devices[i]);
+        for (int j = 0; j < i && !rc; ++j) {          // direct copies between the devices where the box allows them
+            if (devices[j] == devices[i]) continue;
+            int can = 0;
+            if (cudaDeviceCanAccessPeer(&can, devices[i], devices[j]) == cudaSuccess && can) {
+                cudaDeviceEnablePeerAccess(devices[j], 0);
+                DeviceGuard g2(devices[j]);
+                cudaDeviceEnablePeerAccess(devices[i], 0);
+            }
+            cudaGetLastError();                        // "already enabled" is not an error here
+        }
+    }
+    if (!rc) {
+        DeviceGuard g(m->dev[0]);
+        if (cudaEventCreateWithFlags(&m->ev_query, cudaEventDisableTiming) != cudaSuccess)
+            rc = fail(DCI_B200_ERR_CUDA, "cannot create an event on device %d", m->dev[0]);
+    }
+    if (rc) {
+        char keep[sizeof(g_err)];
+        memcpy(keep, g_err, sizeof(keep));
+        dci_b200_mdci_destroy(m);
+        memcpy(g_err, keep, sizeof(keep));
+        return rc;
+    }
+    *out = m;
+    return 0;
+}
+
+int dci_b200_mdci_destroy(dci_b200_mdci_t *m) {
+    if (!m) return 0;
+    for (int i = 0; i < 64; ++i) {
+        if (!m->shard[i] && !m->st[i] && !m->ev[i]) continue;
+        DeviceGuard g(m->dev[i]);
+        if (m->st[i]) { cudaStreamSynchronize(m->st[i]); cudaStreamDestroy(m->st[i]); }
+        if (m->ev[i]) cudaEventDestroy(m->ev[i]);
+        if (m->shard[i]) dci_b200_destroy(m->shard[i]);
+        m->data[i].release(); m->query[i].release(); m->lists[i].release(); m->tmp[i].release();
+    }
+    {
+        DeviceGuard g(m->dev[0]);
+        if (m->ev_query) cudaEventDestroy(m->ev_query);
+        m->gathered.release(); m->q0.release(); m->ids0.release(); m->dists0.release();
+    }
+    delete m;
+    return 0;
+}
+
+int dci_b200_mdci_num_devices(dci_b200_mdci_t *m) { return m ? m->D : 0; }
+
+dci_b200_t *dci_b200_mdci_shard(dci_b200_mdci_t *m, int i) { return (m && i >= 0 && i < m->D) ? m->shard[i] : nullptr; }
+
+long long dci_b200_mdci_data_per_device(dci_b200_mdci_t *m) { return m ? m->dpd : 0; }
+
+int dci_b200_mdci_add(dci_b200_mdci_t *m, const float *h_data, long long num_points, int block_size, int thread_size) {
+    if (int rc = mdci_check(m)) return rc;
+    if (m->num_points > 0)
+        return fail(DCI_B200_ERR_STATE, "the index already holds %lld points; it does not support insertion of more than one array (clear first)", m->num_points);
+    if (!h_data || num_points <= 0) return fail(DCI_B200_ERR_ARG, "null data or no points");
+    const long long dpd = num_points / m->D + 1;                    // the reference's rule, core.py:122
+    if (dpd > 0x7FFFFFFFll) return fail(DCI_B200_ERR_UNSUPPORTED, "a shard of %lld points is too large", dpd);
+    for (int i = 0; i < m->D; ++i) {                                  // everything below is enqueued, device by device
+        const long long lo = std::min(num_points, dpd * i), hi = std::min(num_points, dpd * (i + 1));
+        if (hi <= lo) continue;                                       // a trailing shard without rows stays empty
+        DeviceGuard g(m->dev[i]);
+        const size_t bytes = sizeof(float) * (size_t)(hi - lo) * m->dim;
+        DCI_CUDA(m->data[i].ensure(bytes));
+        DCI_CUDA(cudaMemcpyAsync(m->data[i].p, h_data + (size_t)lo * m->dim, bytes, cudaMemcpyHostToDevice, m->st[i]));
+        if (int rc = dci_b200_add(m->shard[i], (const float *)m->data[i].p, (int)(hi - lo), block_size, thread_size, m->st[i])) {
+            for (int j = 0; j <= i; ++j) dci_b200_clear(m->shard[j]);
+            return rc;
+        }
+    }
+    for (int i = 0; i < m->D; ++i) {
+        DeviceGuard g(m->dev[i]);
+        DCI_CUDA(cudaStreamSynchronize(m->st[i]));
+    }
+    m->num_points = num_points; m->dpd = dpd; m->P = block_size; m->T = thread_size;
+    return 0;
+}
+
+int dci_b200_mdci_clear(dci_b200_mdci_t *m) {
+    if (int rc = mdci_check(m)) return rc;
+    for (int i = 0; i < m->D; ++i)
+        if (int rc = dci_b200_clear(m->shard[i])) return rc;
+    m->num_points = 0; m->dpd = 0;
+    return 0;
+}
+
+int dci_b200_mdci_query(dci_b200_mdci_t *m, const float *d_query, int num_queries, int num_neighbours,
+                        int num_outer_iterations, int max_num_candidates, long long *d_ids, float *d_dists,
+                        void *stream) {
+    if (int rc = mdci_check(m)) return rc;
+    if (m->num_points <= 0) return fail(DCI_B200_ERR_STATE, "the index is empty; add data first");
+    if (num_neighbours <= 0) return fail(DCI_B200_ERR_ARG, "num_neighbours must be positive");   // core.py:131-132
+    if (num_neighbours > dci::kMaxTopK)
+        return fail(DCI_B200_ERR_UNSUPPORTED, "dci_b200_mdci_query serves num_neighbours up to %d", dci::kMaxTopK);
+    if (num_queries < 0) return fail(DCI_B200_ERR_ARG, "num_queries must not be negative");
+    if (num_queries == 0) return 0;
+    if (!d_query || !d_ids || !d_dists) return fail(DCI_B200_ERR_ARG, "null query or output pointer");
+    const int k = num_neighbours, nq = num_queries;
+    const size_t qbytes = sizeof(float) * (size_t)nq * m->dim, lbytes = sizeof(uint64_t) * (size_t)nq * k;
+    cudaStream_t st0 = (cudaStream_t)stream;
+    long long offsets[64];
+    {
+        DeviceGuard g(m->dev[0]);
+        DCI_CUDA(m->gathered.ensure(lbytes * m->D));
+        for (int i = 0; i < m->D; ++i)                                // a shard without rows: every slot empty
+            if (dci_b200_num_points(m->shard[i]) <= 0)
+                DCI_CUDA(cudaMemsetAsync((unsigned long long *)m->gathered.p + (size_t)i * nq * k, 0xFF, lbytes, st0));
+        DCI_CUDA(cudaEventRecord(m->ev_query, st0));                  // the queries are ready from here on
+    }
+    for (int i = 0; i < m->D; ++i) {
+        offsets[i] = m->dpd * i;                                      // core.py:149
+        DeviceGuard g(m->dev[i]);
+        cudaStream_t st = m->st[i];
+        unsigned long long *dst = (unsigned long long *)m->gathered.p + (size_t)i * nq * k;
+        const int n_i = dci_b200_num_points(m->shard[i]);
+        DCI_CUDA(cudaStreamWaitEvent(st, m->ev_query, 0));
+        if (n_i > 0) {
+            const float *q = d_query;
+            if (m->dev[i] != m->dev[0]) {                             // the reference copies the queries to every device, core.py:143
+                DCI_CUDA(m->query[i].ensure(qbytes));
+                DCI_CUDA(cudaMemcpyPeerAsync(m->query[i].p, m->dev[i], d_query, m->dev[0], qbytes, st));
+                q = (const float *)m->query[i].p;
+            }
+            DCI_CUDA(m->lists[i].ensure(lbytes));
+            const int k_i = std::min(k, n_i);                         // a shard shorter than k answers with what it has
+            if (k_i == k) {
+                if (int rc = dci_b200_query_packed(m->shard[i], q, nq, k, num_outer_iterations, max_num_candidates, m->P, m->T,
+                                                   (unsigned long long *)m->lists[i].p, st)) return rc;
+            } else {
+                DCI_CUDA(m->tmp[i].ensure(sizeof(uint64_t) * (size_t)nq * k_i));
+                if (int rc = dci_b200_query_packed(m->shard[i], q, nq, k_i, num_outer_iterations, max_num_candidates, m->P, m->T,
+                                                   (unsigned long long *)m->tmp[i].p, st)) return rc;
+                DCI_CUDA(cudaMemsetAsync(m->lists[i].p, 0xFF, lbytes, st));
+                DCI_CUDA(cudaMemcpy2DAsync(m->lists[i].p, sizeof(uint64_t) * (size_t)k, m->tmp[i].p, sizeof(uint64_t) * (size_t)k_i,
+                                           sizeof(uint64_t) * (size_t)k_i, (size_t)nq, cudaMemcpyDeviceToDevice, st));
+            }
+            DCI_CUDA(cudaMemcpyPeerAsync(dst, m->dev[0], m->lists[i].p, m->dev[i], lbytes, st));
+        }
+        DCI_CUDA(cudaEventRecord(m->ev[i], st));
+    }
+    DeviceGuard g(m->dev[0]);
+    for (int i = 0; i < m->D; ++i) DCI_CUDA(cudaStreamWaitEvent(st0, m->ev[i], 0));
+    return dci_b200_merge_shards_packed((const unsigned long long *)m->gathered.p, m->D, nq, k, offsets, d_ids, d_dists,
+                                        m->dev[0], st0);
+}
+
+int dci_b200_mdci_query_host(dci_b200_mdci_t *m, const float *h_query, int num_queries, int num_neighbours,
+                             int num_outer_iterations, int max_num_candidates, long long *h_ids, float *h_dists) {
+    if (int rc = mdci_check(m)) return rc;
+    if (num_queries < 0) return fail(DCI_B200_ERR_ARG, "num_queries must not be negative");
+    if (num_queries == 0) return 0;
+    if (!h_query || !h_ids || !h_dists) return fail(DCI_B200_ERR_ARG, "null query or output pointer");
+    if (num_neighbours <= 0) return fail(DCI_B200_ERR_ARG, "num_neighbours must be positive");
+    DeviceGuard g(m->dev[0]);
+    const size_t qbytes = sizeof(float) * (size_t)num_queries * m->dim;
+    const size_t n_out = (size_t)num_queries * num_neighbours;
+    DCI_CUDA(m->q0.ensure(qbytes));
+    DCI_CUDA(m->ids0.ensure(n_out * sizeof(long long)));
+    DCI_CUDA(m->dists0.ensure(n_out * sizeof(float)));
+    cudaStream_t st0 = m->st[0];
+    DCI_CUDA(cudaMemcpyAsync(m->q0.p, h_query, qbytes, cudaMemcpyHostToDevice, st0));
+    if (int rc = dci_b200_mdci_query(m, (const float *)m->q0.p, num_queries, num_neighbours, num_outer_iterations,
+                                     max_num_candidates, (long long *)m->ids0.p, (float *)m->dists0.p, st0)) return rc;
+    DCI_CUDA(cudaMemcpyAsync(h_ids, m->ids0.p, n_out * sizeof(long long), cudaMemcpyDeviceToHost, st0));
+    DCI_CUDA(cudaMemcpyAsync(h_dists, m->dists0.p, n_out * sizeof(float), cudaMemcpyDeviceToHost, st0));
+    DCI_CUDA(cudaStreamSynchronize(st0));
     return 0;
 }
 

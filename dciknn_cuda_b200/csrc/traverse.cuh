@@ -76,7 +76,7 @@ struct TraverseParams {
 
 constexpr int kMaxQBatch = 8;                  // queries whose exhaustive distance phases share row loads
 constexpr int kPriWidth = 5;                   // simple indices whose window keys a thread loads together
-constexpr int kPromoPoints = 5;                // points a thread carries through the promotion phase
+constexpr int kPromoPairs = 5;                 // pairs of neighbouring points a thread carries through the promotion phase
 constexpr int kDistChunk = 16;                 // floats of a row staged per step of the distance phase
 constexpr int kDistStride = kDistChunk + 4;    // padded row stride of the staging tile (floats)
 
@@ -86,7 +86,7 @@ struct TraverseLayout {
     size_t cnt_bytes, qvec_bytes, fixed_bytes;
     int nbuckets;
     // "big" region (shared or global): [rank table per composite][union]
-    //   union, ordering view : kA u32[wcap] | bval ValT[wcap] | slot u8[wcap]
+    //   union, ordering view : kA u32[wcap] | bval ValT[wcap] | slot u8[wcap] | bkey u32[wcap]
     //   union, point view    : kenc u32[ppb] | ... | list ValT[ppb] at list_off
     //   union, distance view : top-k 2 x u64[topk_cap] | staging tiles | ... | list (kept)
     size_t rank_bytes, wk_bytes, wv_bytes, ws_bytes, point_bytes, list_bytes, topk_bytes, tile_bytes,
@@ -114,12 +114,36 @@ struct TraverseLayout {
         l.tile_bytes = tiles ? (size_t)(nthreads / 32) * 32 * kDistStride * 4 : 0;
         const size_t need = l.topk_bytes + l.tile_bytes;
         l.list_off = l.point_bytes > need ? l.point_bytes : need;
-        const size_t sort_total = l.wk_bytes + l.wv_bytes + l.ws_bytes;
+        const size_t sort_total = 2 * l.wk_bytes + l.wv_bytes + l.ws_bytes;
         const size_t point_total = l.list_off + l.list_bytes;
         l.big_bytes = l.rank_bytes + (sort_total > point_total ? sort_total : point_total);
         l.fallback_bytes = 2 * l.wk_bytes + 2 * l.wv_bytes;
         return l;
     }
+};
+
+struct TrueTag { static constexpr bool value = true; };
+struct FalseTag { static constexpr bool value = false; };
+
+// Positions of two neighbouring points of one sorted segment, read with one load (the segment
+// starts on an aligned boundary and its padding is zero, see pos_segment_start).  A pair that is
+// not loaded reads as position 0.
+template <typename PosT> struct PosPair;
+template <> struct PosPair<uint16_t> {
+    uint32_t w;
+    __device__ __forceinline__ void load(const uint16_t *p, bool live) {
+        w = live ? __ldg(reinterpret_cast<const uint32_t *>(p)) : 0u;
+    }
+    __device__ __forceinline__ uint32_t first() const { return w & 0xFFFFu; }
+    __device__ __forceinline__ uint32_t second() const { return w >> 16; }
+};
+template <> struct PosPair<uint32_t> {
+    uint2 w;
+    __device__ __forceinline__ void load(const uint32_t *p, bool live) {
+        w = live ? __ldg(reinterpret_cast<const uint2 *>(p)) : make_uint2(0u, 0u);
+    }
+    __device__ __forceinline__ uint32_t first() const { return w.x; }
+    __device__ __forceinline__ uint32_t second() const { return w.y; }
 };
 
 // Sum of v over the CTA, returned to every thread.  scratch: 33 shared words.
@@ -199,7 +223,7 @@ __device__ __forceinline__ float dist_sequential_v8(const float *__restrict__ ro
     const int n8 = dim >> 3;
     int c = 0;
     // two loads in flight per check: a check after every load would expose one memory latency per
-    // 8 coordinates, and four loads do not fit the register budget
+    // 8 coordinates
     for (; c + 2 <= n8; c += 2) {
         if (sq > bound_sq) return -1.0f;
         float a[8], b[8];
@@ -319,6 +343,7 @@ traverse_kernel(const TraverseParams prm) {
     uint32_t *kA = reinterpret_cast<uint32_t *>(uni);
     ValT *bval = reinterpret_cast<ValT *>(uni + lay.wk_bytes);
     uint8_t *slot = reinterpret_cast<uint8_t *>(uni + lay.wk_bytes + lay.wv_bytes);
+    uint32_t *bkey = reinterpret_cast<uint32_t *>(uni + lay.wk_bytes + lay.wv_bytes + lay.ws_bytes);   // keys, bucket by bucket
     // radix-sort fallback buffers (global)
     uint32_t *fb_k0 = reinterpret_cast<uint32_t *>(slab);
     uint32_t *fb_k1 = reinterpret_cast<uint32_t *>(slab + lay.wk_bytes);
@@ -472,7 +497,7 @@ traverse_kernel(const TraverseParams prm) {
                            window_visit_order((int)b2 - woff[ha], nlv[ha], spv[ha]);
                 };
                 auto mark = [&](int slot_) { DCI_PHASE_MARK(slot_) };
-                cta_bucket_place_and_rank<ValT, ValT>(kA, Wm, slot, bval, cnt, lay.nbuckets, scale, s_scratch,
+                cta_bucket_place_and_rank<ValT, ValT>(kA, Wm, slot, bval, bkey, cnt, lay.nbuckets, scale, s_scratch,
                                                       rk, tie_less, mark);
             } else {
                 // many equal priorities: stable radix sort of the windows laid out in visiting order
@@ -492,62 +517,82 @@ traverse_kernel(const TraverseParams prm) {
         }
 
         // ---- 3. promotion iteration and lane of every point; lane-0 promotions listed
-        // Each thread carries kPromoPoints points through all simple indices so that
-        // the per-index constants stay in registers and the position loads of one
-        // index are independent of each other.
-        for (int p0 = 0; p0 < n; p0 += kPromoPoints * blockDim.x) {
-            uint32_t best[kPromoPoints];
+        // Each thread carries kPromoPairs pairs of neighbouring points through all simple indices, so
+        // that the per-index constants stay in registers, one load brings the positions of two points
+        // and the loads of the next index are in flight while this one's ranks are looked up.
+        const uint32_t tmul = 1u << prm.tshift;
+        auto promote = [&](auto t_is_one) {
+            constexpr bool kT1 = decltype(t_is_one)::value;
+            const size_t pstride = (size_t)pos_stride(prm.ppb);
+            const int pair_step = 2 * (int)blockDim.x;
+            for (int p0 = 0; p0 < n; p0 += kPromoPairs * pair_step) {
+                const int pt = p0 + 2 * tid;                       // first point of this thread's pair 0
+                uint32_t best[2 * kPromoPairs];
 #pragma unroll
-            for (int j = 0; j < kPromoPoints; ++j) best[j] = 0xFFFFFFFFu;
-            for (int m = 0; m < L; ++m) {
-                const ValT *rkm = rank + (size_t)m * prm.wcap;
-                uint32_t mx[kPromoPoints];
+                for (int j = 0; j < 2 * kPromoPairs; ++j) best[j] = 0xFFFFFFFFu;
+                for (int m = 0; m < L; ++m) {
+                    const ValT *rkm = rank + (size_t)m * prm.wcap;
+                    const PosT *row = spos + pos_segment_start(b, m * S, I, prm.ppb) + pt;
+                    uint32_t mx[2 * kPromoPairs];
 #pragma unroll
-                for (int j = 0; j < kPromoPoints; ++j) mx[j] = 0u;
-                for (int h = 0; h < S; ++h) {
-                    const int i = m * S + h;
-                    const int2 cb = s_cb[i];
-                    const PosT *row = spos + segment_start(lo, i, I, n);
-                    const ValT *rkb = rkm + cb.y;
-                    uint32_t y[kPromoPoints];
+                    for (int j = 0; j < 2 * kPromoPairs; ++j) mx[j] = 0u;
+                    PosPair<PosT> cur[kPromoPairs], nxt[kPromoPairs];
 #pragma unroll
-                    for (int j = 0; j < kPromoPoints; ++j) {
-                        const int p = p0 + j * blockDim.x + tid;
-                        y[j] = p < n ? (uint32_t)__ldg(row + p) : 0u;
+                    for (int j = 0; j < kPromoPairs; ++j) cur[j].load(row + j * pair_step, pt + j * pair_step < n);
+                    for (int h = 0; h < S; ++h) {
+                        if (h + 1 < S) {
+#pragma unroll
+                            for (int j = 0; j < kPromoPairs; ++j)
+                                nxt[j].load(row + (size_t)(h + 1) * pstride + j * pair_step, pt + j * pair_step < n);
+                        }
+                        const int2 cb = s_cb[m * S + h];
+                        const ValT *rkb = rkm + cb.y;
+#pragma unroll
+                        for (int j = 0; j < kPromoPairs; ++j) {
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const uint32_t x = (e ? cur[j].second() : cur[j].first()) + (uint32_t)cb.x;   // position relative to window 0
+                                uint32_t enc;
+                                if (kT1) {
+                                    enc = (uint32_t)rkb[x];
+                                } else {
+                                    const uint32_t g = __umulhi(x, prm.divT.magic);
+                                    const uint32_t t = x - g * (uint32_t)T;
+                                    enc = (uint32_t)rkb[g] * tmul + t;
+                                }
+                                mx[2 * j + e] = max(mx[2 * j + e], enc);
+                            }
+                        }
+#pragma unroll
+                        for (int j = 0; j < kPromoPairs; ++j) cur[j] = nxt[j];
                     }
 #pragma unroll
-                    for (int j = 0; j < kPromoPoints; ++j) {
-                        const uint32_t x = y[j] + (uint32_t)cb.x;        // position relative to window 0
-                        const uint32_t g = prm.divT.div(x);
-                        const uint32_t t = x - g * (uint32_t)T;
-                        mx[j] = max(mx[j], ((uint32_t)rkb[g] << prm.tshift) | t);
-                    }
+                    for (int j = 0; j < 2 * kPromoPairs; ++j)
+                        if ((mx[j] >> prm.tshift) < (best[j] >> prm.tshift)) best[j] = mx[j];   // ties keep the lower composite
                 }
+                // one reservation per warp for the lane-0 promotions of all its points (every warp of
+                // the CTA appends to the same counter)
+                unsigned m0[2 * kPromoPairs];
+                int total0 = 0;
 #pragma unroll
-                for (int j = 0; j < kPromoPoints; ++j)
-                    if ((mx[j] >> prm.tshift) < (best[j] >> prm.tshift)) best[j] = mx[j];   // ties keep the lower composite
-            }
-            // one reservation per warp for the lane-0 promotions of all its points (every warp of
-            // the CTA appends to the same counter)
-            unsigned m0[kPromoPoints];
-            int total0 = 0;
+                for (int j = 0; j < 2 * kPromoPairs; ++j) {
+                    const int p = pt + (j >> 1) * pair_step + (j & 1);
+                    const bool live = p < n;
+                    if (live) kenc[p] = best[j];
+                    m0[j] = __ballot_sync(0xFFFFFFFFu, live && (best[j] & tmask) == 0u);
+                    total0 += __popc(m0[j]);
+                }
+                int base0 = 0;
+                if (lane == 0 && total0) base0 = atomicAdd(&s_count[0], total0);
+                base0 = __shfl_sync(0xFFFFFFFFu, base0, 0);
 #pragma unroll
-            for (int j = 0; j < kPromoPoints; ++j) {
-                const int p = p0 + j * blockDim.x + tid;
-                const bool live = p < n;
-                if (live) kenc[p] = best[j];
-                m0[j] = __ballot_sync(0xFFFFFFFFu, live && (best[j] & tmask) == 0u);
-                total0 += __popc(m0[j]);
+                for (int j = 0; j < 2 * kPromoPairs; ++j) {
+                    if ((m0[j] >> lane) & 1u) list[base0 + __popc(m0[j] & lanemask_lt())] = (ValT)(best[j] >> prm.tshift);
+                    base0 += __popc(m0[j]);
+                }
             }
-            int base0 = 0;
-            if (lane == 0 && total0) base0 = atomicAdd(&s_count[0], total0);
-            base0 = __shfl_sync(0xFFFFFFFFu, base0, 0);
-#pragma unroll
-            for (int j = 0; j < kPromoPoints; ++j) {
-                if ((m0[j] >> lane) & 1u) list[base0 + __popc(m0[j] & lanemask_lt())] = (ValT)(best[j] >> prm.tshift);
-                base0 += __popc(m0[j]);
-            }
-        }
+        };
+        if (T == 1) promote(TrueTag{}); else promote(FalseTag{});
         __syncthreads();
 
         DCI_PHASE_MARK(3)

@@ -40,6 +40,7 @@ extern "C" {
 #endif
 
 typedef struct dci_b200 dci_b200_t;
+typedef struct dci_b200_mdci dci_b200_mdci_t;   /* one index sharded over several devices, see the end of this file */
 
 enum {
     DCI_B200_OK = 0,
@@ -256,6 +257,44 @@ int dci_b200_merge_shards(const int *d_ids_in, const float *d_dists_in, int num_
 int dci_b200_merge_shards_packed(const unsigned long long *d_packed_in, int num_shards, int num_queries,
                                  int k, const long long *id_offsets, long long *d_ids_out,
                                  float *d_dists_out, int device, void *stream);
+
+/* ---- MDCI: one point set sharded over the devices of one process -------------------------------
+ * Replaces the MDCI class and its native fan-out (dciknn_cuda/core.py:110-169,
+ * _dci_multi_query in src/dci_cuda.cpp:120-134, 182), so that a C or C++ host can run the sharded
+ * query without the Python layer.  (dciknn_cuda_b200.MDCI additionally offers one process per
+ * GPU over torch.distributed.)
+ *
+ * create: one index per entry of `devices` (the same device may appear more than once), each with
+ * its own directions, as the reference's per-device instances have (core.py:117); seeds may be NULL.
+ * dci_b200_mdci_shard returns the index of shard i (owned by the MDCI handle), e.g. for
+ * dci_b200_set_proj / dci_b200_get_proj.
+ * add (replaces MDCI.add, core.py:121-126): h_data is a HOST array [num_points][dim]; shard i
+ * receives rows [i*dpd, (i+1)*dpd), dpd = num_points / D + 1, copies them to its device (the
+ * reference's data[a:b].to(device)) and owns that copy.  A trailing shard without rows stays empty.
+ * All shards are copied, projected and sorted side by side on their own streams.  Synchronous.
+ * query (replaces MDCI.query, core.py:128-157): d_query [num_queries][dim] lives on devices[0] and is
+ * ready in `stream` order; it is copied to the other devices (core.py:143), every shard answers
+ * every query on its own stream, the lists come back to devices[0] as peer copies of 64-bit
+ * (distance, id) keys and are merged there on `stream` (ids offset by dpd * shard, ties to the lower
+ * global id: core.py:149-157).  d_ids int64 / d_dists fp32 [num_queries][num_neighbours] on
+ * devices[0], -1 / +inf in slots no shard fills.  num_neighbours <= 0 is an error as in the reference
+ * (core.py:131-132); num_neighbours up to 1024.  Asynchronous; one call in flight per handle.
+ * query_host: the same from and to host arrays.  Synchronous. */
+int dci_b200_mdci_create(dci_b200_mdci_t **out, int dim, int num_comp_indices, int num_simp_indices,
+                         const int *devices, int num_devices, const unsigned long long *seeds);
+int dci_b200_mdci_destroy(dci_b200_mdci_t *m);
+int dci_b200_mdci_num_devices(dci_b200_mdci_t *m);
+dci_b200_t *dci_b200_mdci_shard(dci_b200_mdci_t *m, int i);
+long long dci_b200_mdci_data_per_device(dci_b200_mdci_t *m);
+int dci_b200_mdci_add(dci_b200_mdci_t *m, const float *h_data, long long num_points, int block_size,
+                      int thread_size);
+int dci_b200_mdci_clear(dci_b200_mdci_t *m);
+int dci_b200_mdci_query(dci_b200_mdci_t *m, const float *d_query, int num_queries, int num_neighbours,
+                        int num_outer_iterations, int max_num_candidates, long long *d_ids,
+                        float *d_dists, void *stream);
+int dci_b200_mdci_query_host(dci_b200_mdci_t *m, const float *h_query, int num_queries,
+                             int num_neighbours, int num_outer_iterations, int max_num_candidates,
+                             long long *h_ids, float *h_dists);
 
 /* Query for callers that must not allocate.  (No counterpart in the reference,
  * which allocates and frees managed and device memory inside every query,

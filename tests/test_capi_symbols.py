@@ -37,3 +37,18 @@ def test_argument_errors_need_no_gpu():
     assert lib.dci_b200_add(None, None, 1, 1, 1, None) == _capi.ERR_ARG
     assert lib.dci_b200_query(None, None, 1, 1, 1, 1, 0, 1, 1, None, None, None) == _capi.ERR_ARG
     assert lib.dci_b200_destroy(None) == 0
+
+
+def test_torch_shim_builds_and_exposes_the_reference_entry_points():
+    """The PyTorch-extension module carries the seven functions of the reference's `_dci_cuda`
+    (src/dci_cuda.cpp:175-183); without a GPU, creating an instance fails loudly."""
+    import pytest
+    import torch  # noqa: F401  (the module links against libtorch)
+    from dciknn_cuda_b200.build import build_torch_shim
+    build_torch_shim()
+    from dciknn_cuda_b200 import _dci_b200
+    for name in ("_dci_new", "_dci_add", "_dci_query", "_dci_multi_query", "_dci_clear", "_dci_reset", "_dci_free"):
+        assert callable(getattr(_dci_b200, name)), name
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            _dci_b200._dci_new(8, 2, 3, 0)
