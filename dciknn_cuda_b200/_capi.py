@@ -41,6 +41,7 @@ SYMBOLS = [
     ("dci_b200_get_phase_cycles", C.c_int, [_vp, _vp]),
     ("dci_b200_launch_count", C.c_longlong, [_vp]),
     ("dci_b200_device_alloc_calls", C.c_longlong, []),
+    ("dci_b200_set_max_ctas", C.c_int, [_vp, C.c_int]),
     ("dci_b200_set_projection", C.c_int, [_vp, C.c_int]),
     ("dci_b200_enable_timing", C.c_int, [_vp, C.c_int]),
     ("dci_b200_get_timing", C.c_int, [_vp, _vp]),

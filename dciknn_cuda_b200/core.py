@@ -398,6 +398,11 @@ class DCI(object):
             raise RuntimeError(_capi.lib().dci_b200_last_error().decode())
         _capi.check(rc)
 
+    def set_max_ctas(self, max_ctas):
+        """Caps the number of CTAs of the traversal kernel (0 = automatic).  For tests: with few CTAs
+        every CTA works through many (query, partition) pairs one after the other."""
+        _capi.check(_capi.lib().dci_b200_set_max_ctas(self._live(), int(max_ctas)))
+
     def enable_timing(self, on=True):
         _capi.check(_capi.lib().dci_b200_enable_timing(self._live(), 1 if on else 0))
 

@@ -243,14 +243,16 @@ __device__ __forceinline__ int bucket_of(uint32_t key_bits, float scale, int las
 // Second half of the counting rank.  Precondition: every key w in [0, W) has
 // been dropped into bucket_of(key[w]) with slot[w] = its arrival number there
 // and cnt[b] = the size of bucket b (all <= kMaxBucket), cnt[nbuckets] = 0.
-// Lists the keys bucket by bucket (bkey: the key, bval: its index), then gives
-// every key its rank in ascending (key, tie order): rank = start of its bucket
-// + number of smaller keys inside the bucket.  The ranking walks the bucket
-// ordered lists, so a warp reads consecutive entries, its counter reads fall on
-// the same or neighbouring words and the bucket mates it compares with lie next
-// to its own entry: the only scattered access left is the store of the rank.
-// tie_less(a, b) orders two key indices whose keys are equal.  rank_out[w]
-// receives the rank.  Ends with a barrier.
+// Lists the key indices bucket by bucket in bval, then gives every key its rank
+// in ascending (key, tie order): rank = start of its bucket + number of smaller
+// keys inside the bucket.  tie_less(a, b) orders two key indices whose keys are
+// equal.  rank_out[w] receives the rank.  Ends with a barrier.
+// bkey (W words, may be null): when given, the keys are listed bucket by bucket
+// too and the ranking walks those lists, so that a warp reads consecutive
+// entries, its counter reads fall on the same or neighbouring words and the
+// bucket mates it compares with lie next to its own entry; the only scattered
+// access left is the store of the rank.  Without it every key looks its bucket
+// mates up through bval.
 template <typename ValT, typename CntT, typename TieLess, typename Mark>
 __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, int W, const uint8_t *slot,
                                                           ValT *bval, uint32_t *bkey, CntT *cnt, int nbuckets,
@@ -259,25 +261,53 @@ __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, i
     const int tid = threadIdx.x, last = nbuckets - 1;
     cta_scan_counters(cnt, nbuckets + 1, scratch);           // cnt[b] = start of bucket b, cnt[nbuckets] = W
     mark(8);
-    for (int w = tid; w < W; w += blockDim.x) {
-        const uint32_t k = key[w];
-        const uint32_t dest = (uint32_t)cnt[bucket_of(k, scale, last)] + (uint32_t)slot[w];
-        bval[dest] = (ValT)w;
-        bkey[dest] = k;
+    if (bkey) {
+        for (int w = tid; w < W; w += blockDim.x) {
+            const uint32_t k = key[w];
+            const uint32_t dest = (uint32_t)cnt[bucket_of(k, scale, last)] + (uint32_t)slot[w];
+            bval[dest] = (ValT)w;
+            bkey[dest] = k;
+        }
+        __syncthreads();
+        mark(9);
+        for (int j = tid; j < W; j += blockDim.x) {
+            const uint32_t k = bkey[j];
+            const int b = bucket_of(k, scale, last);
+            const uint32_t lo = cnt[b], hi = cnt[b + 1];
+            uint32_t r = lo;
+            for (uint32_t j2 = lo; j2 < hi; ++j2) {
+                const uint32_t k2 = bkey[j2];
+                if (k2 < k) ++r;
+                else if (k2 == k && j2 != (uint32_t)j && tie_less((uint32_t)bval[j2], (uint32_t)bval[j])) ++r;
+            }
+            rank_out[bval[j]] = (ValT)r;
+        }
+        __syncthreads();
+        return;
     }
+    for (int w = tid; w < W; w += blockDim.x)
+        bval[(uint32_t)cnt[bucket_of(key[w], scale, last)] + (uint32_t)slot[w]] = (ValT)w;
     __syncthreads();
     mark(9);
-    for (int j = tid; j < W; j += blockDim.x) {
-        const uint32_t k = bkey[j];
+    for (int w = tid; w < W; w += blockDim.x) {
+        const uint32_t k = key[w];
         const int b = bucket_of(k, scale, last);
         const uint32_t lo = cnt[b], hi = cnt[b + 1];
         uint32_t r = lo;
-        for (uint32_t j2 = lo; j2 < hi; ++j2) {
-            const uint32_t k2 = bkey[j2];
-            if (k2 < k) ++r;
-            else if (k2 == k && j2 != (uint32_t)j && tie_less((uint32_t)bval[j2], (uint32_t)bval[j])) ++r;
+        if (hi - lo > 1)                                 // alone in its bucket: the rank is the bucket start
+        for (uint32_t j0 = lo; j0 < hi; j0 += 4) {      // four bucket mates at a time: independent loads
+            uint32_t other[4], kj[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) other[u] = j0 + u < hi ? (uint32_t)bval[j0 + u] : (uint32_t)w;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) kj[u] = key[other[u]];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                if (kj[u] < k) ++r;
+                else if (kj[u] == k && other[u] != (uint32_t)w && tie_less(other[u], (uint32_t)w)) ++r;
+            }
         }
-        rank_out[bval[j]] = (ValT)r;
+        rank_out[w] = (ValT)r;
     }
     __syncthreads();
 }

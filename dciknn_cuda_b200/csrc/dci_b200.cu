@@ -115,6 +115,7 @@ struct dci_b200 {
     const float *d_data = nullptr;       // borrowed
     float *d_proj = nullptr;             // [L*S][dim]
     Buf keys, ids, pos, keysT;           // sorted index, inverse positions, stride-T keys: L*S*N entries each, partition-major (segment_start)
+    int max_ctas = 0;                    // > 0: cap on the traversal grid (dci_b200_set_max_ctas)
     Buf tmp_keys, qproj, part_topk, scratch, merge_scratch, stats, phases, hq, hids, hdists, qbound;
     int distance_bound = 1;              // 1: share a per-query distance bound between partitions
     int stats_on = 0, stats_nq = 0, phases_valid = 0;
@@ -256,14 +257,16 @@ int launch_build(dci_b200 *h, const float *d_unsorted, cudaStream_t st) {
 // of a composite index (so that most buckets hold at most one window) while the
 // whole work item still fits shared memory, else fewer.
 template <typename ValT>
-int pick_buckets(dci_b200 *h, const dci::TraverseParams &prm, int nthreads, size_t static_smem) {
-    const int choices[3] = {2 * prm.wcap, prm.wcap, prm.wcap / 2};
-    for (int c = 0; c < 3; ++c) {
+int pick_buckets(dci_b200 *h, dci::TraverseParams &prm, int nthreads, size_t static_smem) {
+    // first choice: twice as many buckets as windows and a bucket-ordered copy of the keys
+    const int choices[4] = {2 * prm.wcap, 2 * prm.wcap, prm.wcap, prm.wcap / 2};
+    for (int c = 0; c < 4; ++c) {
         const int nb = std::min(std::max(choices[c], 64), 1 << 20);
         const auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_global ? 0 : prm.topk_cap, prm.L,
-                                                         prm.wcap, prm.ppb, nb, prm.vec4 && !prm.vec8);
-        if (lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin) return nb;
+                                                         prm.wcap, prm.ppb, nb, prm.vec4 && !prm.vec8, c == 0);
+        if (lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin) { prm.bkey = c == 0 ? 1 : 0; return nb; }
     }
+    prm.bkey = 0;
     return std::min(std::max(prm.wcap / 2, 64), 16384);
 }
 
@@ -275,12 +278,12 @@ int launch_traverse(dci_b200 *h, dci::TraverseParams prm, int nthreads, cudaStre
     prm.nbuckets = pick_buckets<ValT>(h, prm, nthreads, static_smem);
     const int cap_smem = prm.topk_global ? 0 : prm.topk_cap;
     auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, cap_smem, prm.L, prm.wcap, prm.ppb, prm.nbuckets,
-                                               prm.vec4 && !prm.vec8);
+                                               prm.vec4 && !prm.vec8, prm.bkey != 0);
     if (lay.fixed_bytes + static_smem > h->smem_optin)
         return fail(DCI_B200_ERR_UNSUPPORTED, "dim=%d with k=%d needs %zu bytes of shared memory per CTA, more than the device offers",
                     prm.dim, prm.knn, lay.fixed_bytes + static_smem);
     const bool smem = lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin;
-    if (!smem) lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, cap_smem, prm.L, prm.wcap, prm.ppb, prm.nbuckets, false);
+    if (!smem) lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, cap_smem, prm.L, prm.wcap, prm.ppb, prm.nbuckets, false, prm.bkey != 0);
     const size_t dyn = smem ? lay.fixed_bytes + lay.big_bytes : lay.fixed_bytes;
     // queries per CTA pass: the dense distance pass needs, per query, a pair of selection buffers
     // and the query vector inside the shared "big" region
@@ -298,7 +301,8 @@ int launch_traverse(dci_b200 *h, dci::TraverseParams prm, int nthreads, cudaStre
     const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));
     h->last_qbatch = prm.qbatch;
     const long long nwork = (long long)((prm.nq + prm.qbatch - 1) / prm.qbatch) * prm.num_parts;
-    const unsigned grid = (unsigned)std::min<long long>(nwork, (long long)h->sm_count * per_sm);
+    unsigned grid = (unsigned)std::min<long long>(nwork, (long long)h->sm_count * per_sm);
+    if (h->max_ctas > 0) grid = std::min(grid, (unsigned)h->max_ctas);
     DCI_CUDA(h->scratch.ensure(per_cta * grid));
     prm.gscratch = (unsigned char *)h->scratch.p;
     prm.gscratch_per_cta = per_cta;
@@ -816,6 +820,13 @@ long long dci_b200_launch_count(dci_b200_t *h) { return h ? h->launches : 0; }
 
 long long dci_b200_device_alloc_calls(void) { return g_alloc_calls.load(); }
 
+int dci_b200_set_max_ctas(dci_b200_t *h, int max_ctas) {
+    if (int rc = check_handle(h)) return rc;
+    if (max_ctas < 0) return fail(DCI_B200_ERR_ARG, "max_ctas must not be negative");
+    h->max_ctas = max_ctas;
+    return 0;
+}
+
 int dci_b200_set_projection(dci_b200_t *h, int mode) {
     if (int rc = check_handle(h)) return rc;
     if (mode < 0 || mode > 3)
@@ -1171,11 +1182,11 @@ int query_noalloc_impl(dci_b200 *h, dci::TraverseParams prm, int nthreads, unsig
     const size_t static_smem = fa.sharedSizeBytes;
     prm.nbuckets = pick_buckets<ValT>(h, prm, nthreads, static_smem);
     auto lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, prm.nbuckets,
-                                               prm.vec4 && !prm.vec8);
+                                               prm.vec4 && !prm.vec8, prm.bkey != 0);
     if (lay.fixed_bytes + static_smem > h->smem_optin)
         return fail(DCI_B200_ERR_UNSUPPORTED, "dim=%d needs more shared memory per CTA than the device offers", prm.dim);
     const bool smem = lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin;
-    if (!smem) lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, prm.nbuckets, false);
+    if (!smem) lay = dci::TraverseLayout<ValT>::make(nthreads, prm.dim, prm.topk_cap, prm.L, prm.wcap, prm.ppb, prm.nbuckets, false, prm.bkey != 0);
     const size_t dyn = smem ? lay.fixed_bytes + lay.big_bytes : lay.fixed_bytes;
     const size_t per_cta = align256(lay.fallback_bytes + (smem ? 0 : lay.big_bytes));
     const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + static_smem + 1024), 2048 / nthreads));

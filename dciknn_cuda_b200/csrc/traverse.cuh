@@ -59,6 +59,7 @@ struct TraverseParams {
     int knn, max_cand;
     int wcap;                  // capacity of one composite's window list
     int nbuckets;              // value buckets of the window ordering
+    int bkey;                  // 1: the ordering keeps a bucket-ordered copy of the keys (needs wcap more words)
     int kpart;                 // length of a partition's result list: min(knn, ppb)
     int topk_cap;              // power of two >= kpart + blockDim.x
     int topk_global;           // 1: the top-k buffers live in the CTA's global slab (large k)
@@ -76,7 +77,6 @@ struct TraverseParams {
 
 constexpr int kMaxQBatch = 8;                  // queries whose exhaustive distance phases share row loads
 constexpr int kPriWidth = 5;                   // simple indices whose window keys a thread loads together
-constexpr int kPromoPairs = 5;                 // pairs of neighbouring points a thread carries through the promotion phase
 constexpr int kDistChunk = 16;                 // floats of a row staged per step of the distance phase
 constexpr int kDistStride = kDistChunk + 4;    // padded row stride of the staging tile (floats)
 
@@ -95,7 +95,7 @@ struct TraverseLayout {
     size_t fallback_bytes;
     __host__ __device__ static size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
     __host__ __device__ static TraverseLayout make(int nthreads, int dim, int topk_cap, int L,
-                                                   int wcap, int ppb, int nbuckets, bool tiles) {
+                                                   int wcap, int ppb, int nbuckets, bool tiles, bool bkey) {
         TraverseLayout l;
         const size_t radix_hist = (size_t)256 * (nthreads / 32) * sizeof(ValT);
         l.nbuckets = nbuckets;
@@ -114,7 +114,7 @@ struct TraverseLayout {
         l.tile_bytes = tiles ? (size_t)(nthreads / 32) * 32 * kDistStride * 4 : 0;
         const size_t need = l.topk_bytes + l.tile_bytes;
         l.list_off = l.point_bytes > need ? l.point_bytes : need;
-        const size_t sort_total = 2 * l.wk_bytes + l.wv_bytes + l.ws_bytes;
+        const size_t sort_total = (bkey ? 2 : 1) * l.wk_bytes + l.wv_bytes + l.ws_bytes;
         const size_t point_total = l.list_off + l.list_bytes;
         l.big_bytes = l.rank_bytes + (sort_total > point_total ? sort_total : point_total);
         l.fallback_bytes = 2 * l.wk_bytes + 2 * l.wv_bytes;
@@ -122,6 +122,7 @@ struct TraverseLayout {
     }
 };
 
+template <int V> struct IntTag { static constexpr int value = V; };
 struct TrueTag { static constexpr bool value = true; };
 struct FalseTag { static constexpr bool value = false; };
 
@@ -332,7 +333,7 @@ traverse_kernel(const TraverseParams prm) {
     const int L = prm.L, S = prm.S, T = prm.T, I = L * S, N = prm.N, dim = prm.dim;
     const TraverseLayout<ValT> lay =
         TraverseLayout<ValT>::make(blockDim.x, dim, prm.topk_global ? 0 : prm.topk_cap, L, prm.wcap, prm.ppb,
-                                   prm.nbuckets, SMEM && prm.vec4 && !prm.vec8);
+                                   prm.nbuckets, SMEM && prm.vec4 && !prm.vec8, prm.bkey != 0);
     ValT *cnt = reinterpret_cast<ValT *>(dyn_smem);                    // bucket counters / radix histogram
     float *qvec = reinterpret_cast<float *>(dyn_smem + lay.cnt_bytes);
     unsigned char *slab = prm.gscratch + (size_t)blockIdx.x * prm.gscratch_per_cta;
@@ -343,7 +344,8 @@ traverse_kernel(const TraverseParams prm) {
     uint32_t *kA = reinterpret_cast<uint32_t *>(uni);
     ValT *bval = reinterpret_cast<ValT *>(uni + lay.wk_bytes);
     uint8_t *slot = reinterpret_cast<uint8_t *>(uni + lay.wk_bytes + lay.wv_bytes);
-    uint32_t *bkey = reinterpret_cast<uint32_t *>(uni + lay.wk_bytes + lay.wv_bytes + lay.ws_bytes);   // keys, bucket by bucket
+    uint32_t *bkey = prm.bkey ? reinterpret_cast<uint32_t *>(uni + lay.wk_bytes + lay.wv_bytes + lay.ws_bytes)
+                              : nullptr;                                                               // keys, bucket by bucket
     // radix-sort fallback buffers (global)
     uint32_t *fb_k0 = reinterpret_cast<uint32_t *>(slab);
     uint32_t *fb_k1 = reinterpret_cast<uint32_t *>(slab + lay.wk_bytes);
@@ -517,38 +519,40 @@ traverse_kernel(const TraverseParams prm) {
         }
 
         // ---- 3. promotion iteration and lane of every point; lane-0 promotions listed
-        // Each thread carries kPromoPairs pairs of neighbouring points through all simple indices, so
+        // Each thread carries a few pairs of neighbouring points through all simple indices, so
         // that the per-index constants stay in registers, one load brings the positions of two points
         // and the loads of the next index are in flight while this one's ranks are looked up.
         const uint32_t tmul = 1u << prm.tshift;
-        auto promote = [&](auto t_is_one) {
+        // one pass: this thread's kPairs pairs, pair j = points p0 + 2 * (j * blockDim + tid) and the next one
+        auto promote_pass = [&](auto t_is_one, auto pairs_tag, const int p0) {
             constexpr bool kT1 = decltype(t_is_one)::value;
+            constexpr int kPairs = decltype(pairs_tag)::value;
             const size_t pstride = (size_t)pos_stride(prm.ppb);
             const int pair_step = 2 * (int)blockDim.x;
-            for (int p0 = 0; p0 < n; p0 += kPromoPairs * pair_step) {
+            {
                 const int pt = p0 + 2 * tid;                       // first point of this thread's pair 0
-                uint32_t best[2 * kPromoPairs];
+                uint32_t best[2 * kPairs];
 #pragma unroll
-                for (int j = 0; j < 2 * kPromoPairs; ++j) best[j] = 0xFFFFFFFFu;
+                for (int j = 0; j < 2 * kPairs; ++j) best[j] = 0xFFFFFFFFu;
                 for (int m = 0; m < L; ++m) {
                     const ValT *rkm = rank + (size_t)m * prm.wcap;
                     const PosT *row = spos + pos_segment_start(b, m * S, I, prm.ppb) + pt;
-                    uint32_t mx[2 * kPromoPairs];
+                    uint32_t mx[2 * kPairs];
 #pragma unroll
-                    for (int j = 0; j < 2 * kPromoPairs; ++j) mx[j] = 0u;
-                    PosPair<PosT> cur[kPromoPairs], nxt[kPromoPairs];
+                    for (int j = 0; j < 2 * kPairs; ++j) mx[j] = 0u;
+                    PosPair<PosT> cur[kPairs], nxt[kPairs];
 #pragma unroll
-                    for (int j = 0; j < kPromoPairs; ++j) cur[j].load(row + j * pair_step, pt + j * pair_step < n);
+                    for (int j = 0; j < kPairs; ++j) cur[j].load(row + j * pair_step, pt + j * pair_step < n);
                     for (int h = 0; h < S; ++h) {
                         if (h + 1 < S) {
 #pragma unroll
-                            for (int j = 0; j < kPromoPairs; ++j)
+                            for (int j = 0; j < kPairs; ++j)
                                 nxt[j].load(row + (size_t)(h + 1) * pstride + j * pair_step, pt + j * pair_step < n);
                         }
                         const int2 cb = s_cb[m * S + h];
                         const ValT *rkb = rkm + cb.y;
 #pragma unroll
-                        for (int j = 0; j < kPromoPairs; ++j) {
+                        for (int j = 0; j < kPairs; ++j) {
 #pragma unroll
                             for (int e = 0; e < 2; ++e) {
                                 const uint32_t x = (e ? cur[j].second() : cur[j].first()) + (uint32_t)cb.x;   // position relative to window 0
@@ -564,18 +568,18 @@ traverse_kernel(const TraverseParams prm) {
                             }
                         }
 #pragma unroll
-                        for (int j = 0; j < kPromoPairs; ++j) cur[j] = nxt[j];
+                        for (int j = 0; j < kPairs; ++j) cur[j] = nxt[j];
                     }
 #pragma unroll
-                    for (int j = 0; j < 2 * kPromoPairs; ++j)
+                    for (int j = 0; j < 2 * kPairs; ++j)
                         if ((mx[j] >> prm.tshift) < (best[j] >> prm.tshift)) best[j] = mx[j];   // ties keep the lower composite
                 }
                 // one reservation per warp for the lane-0 promotions of all its points (every warp of
                 // the CTA appends to the same counter)
-                unsigned m0[2 * kPromoPairs];
+                unsigned m0[2 * kPairs];
                 int total0 = 0;
 #pragma unroll
-                for (int j = 0; j < 2 * kPromoPairs; ++j) {
+                for (int j = 0; j < 2 * kPairs; ++j) {
                     const int p = pt + (j >> 1) * pair_step + (j & 1);
                     const bool live = p < n;
                     if (live) kenc[p] = best[j];
@@ -586,10 +590,23 @@ traverse_kernel(const TraverseParams prm) {
                 if (lane == 0 && total0) base0 = atomicAdd(&s_count[0], total0);
                 base0 = __shfl_sync(0xFFFFFFFFu, base0, 0);
 #pragma unroll
-                for (int j = 0; j < 2 * kPromoPairs; ++j) {
+                for (int j = 0; j < 2 * kPairs; ++j) {
                     if ((m0[j] >> lane) & 1u) list[base0 + __popc(m0[j] & lanemask_lt())] = (ValT)(best[j] >> prm.tshift);
                     base0 += __popc(m0[j]);
                 }
+            }
+        };
+        // a pass of several pairs per thread while the points still to do fill most of it, passes of
+        // one pair for the rest and for small partitions (32-bit positions take two registers a pair,
+        // so their large pass has fewer pairs)
+        auto promote = [&](auto t_is_one) {
+            const int pair_step = 2 * (int)blockDim.x;
+            for (int p0 = 0; p0 < n;) {
+                const int units = (n - p0 + pair_step - 1) / pair_step;
+                // pairs of the large pass; none where the registers are needed elsewhere (query groups)
+                constexpr int kBig = BATCH ? 0 : (sizeof(PosT) != 2 ? 2 : (SMEM ? 5 : 4));
+                if (kBig > 1 && units >= kBig - 1) { promote_pass(t_is_one, IntTag<(kBig > 1 ? kBig : 1)>{}, p0); p0 += kBig * pair_step; }
+                else { promote_pass(t_is_one, IntTag<1>{}, p0); p0 += pair_step; }
             }
         };
         if (T == 1) promote(TrueTag{}); else promote(FalseTag{});

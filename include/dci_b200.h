@@ -211,6 +211,11 @@ long long dci_b200_launch_count(dci_b200_t *h);
  * that a call allocated nothing: the count is the same before and after. */
 long long dci_b200_device_alloc_calls(void);
 
+/* Caps the number of CTAs of the traversal kernel (0, the default: as many as the device keeps
+ * resident).  A diagnostic: with few CTAs each one works through many (query, partition) pairs in a
+ * row, so tests reach whatever a CTA keeps from one pair to the next. */
+int dci_b200_set_max_ctas(dci_b200_t *h, int max_ctas);
+
 /* How data and queries are projected on the directions (replaces the
  * cublasSgemm calls of src/util_kernel.cu:45-80).  0 (default): exact fp32, one
  * fused multiply-add per term in ascending coordinate order -- the path every

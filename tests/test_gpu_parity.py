@@ -17,11 +17,12 @@ def _dci(c, **kw):
     return DCI(c["data"].shape[1], c["L"], c["S"], c["P"], c["T"], 0, proj=torch.from_numpy(c["proj"]), **kw)
 
 
-def _run_both(c, stats=True):
+def _run_both(c, stats=True, max_ctas=0):
     dev = torch.device("cuda", 0)
     data = torch.from_numpy(c["data"]).to(dev)
     query = torch.from_numpy(c["query"]).to(dev)
     g = _dci(c)
+    g.set_max_ctas(max_ctas)
     g.add(data)
     if stats:
         g.enable_work_stats(True)
@@ -101,10 +102,13 @@ def test_index_build_matches_oracle(N, P):
     assert np.array_equal(keys.numpy().view(np.uint32), okeys.view(np.uint32))
 
 
+@pytest.mark.parametrize("max_ctas", [0, 1])
 @pytest.mark.parametrize("row", cases.EDGE_CASES, ids=[r[0] for r in cases.EDGE_CASES])
-def test_query_edge_cases(row):
+def test_query_edge_cases(row, max_ctas):
+    """max_ctas = 1: one CTA takes every (query, partition) pair in turn, so nothing it keeps in shared
+    memory from one pair may leak into the next."""
     c = cases.edge_case(row)
-    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
+    _, _, ids, dists, oi, od, gs, os_ = _run_both(c, max_ctas=max_ctas)
     _assert_same(ids, dists, oi, od, gs, os_, c["name"], _limits(c))
 
 
@@ -118,11 +122,12 @@ def test_example_configuration_is_exact_knn():
     assert np.array_equal(ids, bi) and np.array_equal(dists.view(np.uint32), bd.view(np.uint32))
 
 
-def test_c2_shaped_partitions():
+@pytest.mark.parametrize("max_ctas", [0, 3])
+def test_c2_shaped_partitions(max_ctas):
     """configs[1] cut down to 4 partitions of 10 000 points (shared-memory path, u16 ranks)."""
     c = cases.c2_shaped()
     c["max_cand"] = None
-    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
+    _, _, ids, dists, oi, od, gs, os_ = _run_both(c, max_ctas=max_ctas)
     _assert_same(ids, dists, oi, od, gs, os_, "c2-shaped")
     assert (os_[:, :, 5] == 0).all()          # the quota stops every partition before it runs out
 
@@ -135,8 +140,9 @@ def test_shapes_of_the_other_benchmark_configurations(shape):
     c = {"high_dim": lambda: cases.high_dim_shaped(n=6000, nq=12, P=3),
          "mixture": lambda: cases.mixture_shaped(n=30000, nq=24, P=3),
          "large_k": lambda: cases.large_k_shaped(n=4800, nq=8, P=4)}[shape]()
-    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
-    _assert_same(ids, dists, oi, od, gs, os_, shape, _limits(c))
+    for max_ctas in (0, 2):
+        _, _, ids, dists, oi, od, gs, os_ = _run_both(c, max_ctas=max_ctas)
+        _assert_same(ids, dists, oi, od, gs, os_, shape, _limits(c))
 
 
 def test_large_partition_global_scratch_path():
@@ -144,8 +150,9 @@ def test_large_partition_global_scratch_path():
     rng = np.random.default_rng(3)
     c = dict(data=cases.latent_linear(rng, 30000, 16, 32, 0.01), query=cases.latent_linear(rng, 6, 16, 32, 0.01),
              L=2, S=4, P=1, T=10, k=10, outer=5000, max_cand=None, proj=cases.unit_rows(rng, 8, 32))
-    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
-    _assert_same(ids, dists, oi, od, gs, os_, "global-scratch")
+    for max_ctas in (0, 1):
+        _, _, ids, dists, oi, od, gs, os_ = _run_both(c, max_ctas=max_ctas)
+        _assert_same(ids, dists, oi, od, gs, os_, "global-scratch")
 
 
 def test_wide_rank_path():
@@ -153,8 +160,9 @@ def test_wide_rank_path():
     rng = np.random.default_rng(4)
     c = dict(data=cases.latent_linear(rng, 20000, 8, 16, 0.01), query=cases.latent_linear(rng, 4, 8, 16, 0.01),
              L=1, S=4, P=1, T=1, k=5, outer=5000, max_cand=None, proj=cases.unit_rows(rng, 4, 16))
-    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
-    _assert_same(ids, dists, oi, od, gs, os_, "wide-rank")
+    for max_ctas in (0, 1):
+        _, _, ids, dists, oi, od, gs, os_ = _run_both(c, max_ctas=max_ctas)
+        _assert_same(ids, dists, oi, od, gs, os_, "wide-rank")
 
 
 def test_default_k_returns_every_point():

@@ -48,6 +48,13 @@ def test_random_configurations_match_the_oracle(seed):
         oi, od = o.query(query, p["k"], p["outer"], p["mc"])
         assert np.array_equal(ids.cpu().numpy(), oi), (c, p)
         assert np.array_equal(dists.cpu().numpy().view(np.uint32), od.view(np.uint32)), (c, p)
+        # the same with all work items on two CTAs: every CTA then takes many (query, partition) pairs in
+        # turn, so whatever it keeps in shared memory from one pair must not leak into the next
+        g.set_max_ctas(2)
+        ids, dists = g.query(torch.from_numpy(query).cuda(), p["k"], p["outer"], max_num_candidates=p["mc"],
+                             return_int_ids=True)
+        assert np.array_equal(ids.cpu().numpy(), oi), ("two CTAs", c, p)
+        assert np.array_equal(dists.cpu().numpy().view(np.uint32), od.view(np.uint32)), ("two CTAs", c, p)
         g.free()
 
 
