@@ -654,7 +654,22 @@ static int query_impl(dci_b200_t *h, const float *d_query, int num_queries, int 
         }
         if (timing) DCI_CUDA(cudaEventRecord(h->ev[2], st));
         int rc;
-        if (prm.ppb <= 65535)
+        // partitions of at most 32 points with at most 32 windows per composite index: one warp per
+        // (query, partition) pair instead of one CTA (per-phase cycle counters exist only in the CTA
+        // kernel, and the warp kernel keeps statistics for at most two composite indices)
+        const bool small = h->ppb <= 32 && prm.wcap <= 32 && h->S <= 32 && !blind && !prm.topk_global &&
+                           !(h->stats_on & 2) && (!(h->stats_on & 1) || h->L <= 2);
+        if (small) {
+            const long long nwork = (long long)prm.nq * prm.num_parts;
+            unsigned grid = (unsigned)std::min<long long>((nwork + dci::kSmallWarps - 1) / dci::kSmallWarps,
+                                                          (long long)h->sm_count * 8);
+            if (h->max_ctas > 0) grid = std::min(grid, (unsigned)h->max_ctas);
+            dci::traverse_small_kernel<<<grid, dci::kSmallWarps * 32, 0, st>>>(prm);
+            h->launches++;
+            h->last_qbatch = 1;
+            DCI_CUDA(cudaGetLastError());
+            rc = 0;
+        } else if (prm.ppb <= 65535)
             rc = (prm.wcap <= 65535) ? launch_traverse<uint16_t, uint16_t>(h, prm, nthreads, st)
                                      : launch_traverse<uint32_t, uint16_t>(h, prm, nthreads, st);
         else

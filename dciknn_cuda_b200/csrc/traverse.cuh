@@ -1040,3 +1040,179 @@ __global__ void merge_shards_sorted_kernel(const int *__restrict__ ids_in, const
 }
 
 }  // namespace dci
+
+namespace dci {
+
+// Small partitions: one WARP per (query, partition) work item, no CTA-wide barrier.
+// Same computation as traverse_kernel (steps 1-5 of the comment at the top of this
+// file), for partitions of at most 32 points whose composite indices have at most
+// 32 windows each and at most 32 simple indices: lane = point, lane = window and
+// lane = simple index in turn, everything else moves through shuffles.  The
+// reference's own example (2 000 points in 100 partitions of 20, 7 simple indices
+// per composite index, windows of 10) is of this kind; traverse_kernel spends its
+// time there on barriers of a CTA that has almost nothing to do.
+constexpr int kSmallWarps = 8;        // warps (work items in flight) per CTA
+
+__global__ void __launch_bounds__(kSmallWarps * 32)
+traverse_small_kernel(const TraverseParams prm) {
+    const int lane = threadIdx.x & 31;
+    const unsigned full = 0xFFFFFFFFu;
+    const int L = prm.L, S = prm.S, T = prm.T, I = L * S, dim = prm.dim;
+    const uint16_t *spos = reinterpret_cast<const uint16_t *>(prm.spos);
+    const uint32_t tmask = (1u << prm.tshift) - 1u;
+    const long long nwork = (long long)prm.nq * prm.num_parts;
+    const long long nwarps = (long long)gridDim.x * kSmallWarps;
+    for (long long wi = (long long)blockIdx.x * kSmallWarps + (threadIdx.x >> 5); wi < nwork; wi += nwarps) {
+        const int b = (int)(wi / prm.nq), ql = (int)(wi % prm.nq), q = prm.q0 + ql;
+        const long long lo = (long long)b * prm.ppb;
+        const int n = (int)min((long long)prm.ppb, (long long)prm.N - lo);
+        uint32_t best = 0xFFFFFFFFu;             // this lane's point: promotion iteration << tshift | lane of the window
+        int maxW = 0;
+        uint32_t rank_a = 0xFFFFFFFFu, rank_b = 0xFFFFFFFFu;   // rank of this lane's window in the first two composite indices (statistics)
+        int span_a = 0, span_b = 0;                            // in-range positions of that window
+        for (int m = 0; m < L; ++m) {
+            // ---- 1. split positions: lane h keeps the constants of simple index h of this composite
+            int my_nl = 0, my_cnt = 0, my_c = 0, my_sp = 0;
+            float my_qp = 0.0f;
+            for (int h = 0; h < S; ++h) {
+                const int i = m * S + h;
+                const float qp = __ldg(prm.qproj + (size_t)i * prm.nq_total + q);
+                const float key = lane < n ? __ldg(prm.skeys + segment_start(lo, i, I, n) + lane) : 0.0f;
+                const int s = __popc(__ballot_sync(full, lane < n && key < qp)) - 1;     // last position with key < q
+                if (lane == h) {
+                    my_nl = (s + 1 + T - 1) / T;
+                    const int nr = (n + T - 2 - s + T - 1) / T;
+                    my_cnt = my_nl + nr;
+                    my_c = my_nl * T - s - 1;
+                    my_sp = (s == n - 1 && nr > 0) ? 1 : 0;
+                    my_qp = qp;
+                }
+            }
+            // first window of every simple index inside the composite's window list (exclusive scan over lanes)
+            int my_off = my_cnt;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int t = __shfl_up_sync(full, my_off, o);
+                if (lane >= o) my_off += t;
+            }
+            const int W = __shfl_sync(full, my_off, 31);
+            my_off -= my_cnt;
+            maxW = max(maxW, W);
+            // ---- 2. lane w = window w: its simple index, priority and place in the visiting order
+            int wh = 0;
+            for (int h = 1; h < S; ++h) wh += (__shfl_sync(full, my_off, h) <= lane) ? 1 : 0;
+            const int w_off = __shfl_sync(full, my_off, wh), w_nl = __shfl_sync(full, my_nl, wh);
+            const int w_c = __shfl_sync(full, my_c, wh), w_sp = __shfl_sync(full, my_sp, wh);
+            const float w_qp = __shfl_sync(full, my_qp, wh);
+            uint64_t okey = ~0ull;                // (priority, simple index, order inside the index): the visiting order
+            int span = 0;
+            if (lane < W) {
+                const int g = lane - w_off, start = g * T - w_c;
+                const int at = min(max(start, 0), n - 1);
+                const float kv = __ldg(prm.skeys + segment_start(lo, m * S + wh, I, n) + at);
+                okey = ((uint64_t)__float_as_uint(fabsf(kv - w_qp)) << 32) |
+                       (uint32_t)((wh << 8) | window_visit_order(g, w_nl, w_sp));
+                span = max(0, min(start + T, n) - max(start, 0));
+            }
+            uint32_t rk = 0u;                     // rank = number of windows that come earlier
+            for (int j = 0; j < W; ++j) rk += (__shfl_sync(full, okey, j) < okey) ? 1u : 0u;
+            if (m == 0) { rank_a = lane < W ? rk : 0xFFFFFFFFu; span_a = span; }
+            if (m == 1) { rank_b = lane < W ? rk : 0xFFFFFFFFu; span_b = span; }
+            // ---- 3. lane p = point p: the iteration at which its last simple index visits it
+            uint32_t mx = 0u;
+            for (int h = 0; h < S; ++h) {
+                const int i = m * S + h;
+                const uint32_t y = lane < n ? (uint32_t)__ldg(spos + pos_segment_start(b, i, I, prm.ppb) + lane) : 0u;
+                const uint32_t x = y + (uint32_t)__shfl_sync(full, my_c, h);
+                const uint32_t g = prm.divT.div(x);
+                const uint32_t t = x - g * (uint32_t)T;
+                const uint32_t r = __shfl_sync(full, rk, (__shfl_sync(full, my_off, h) + (int)g) & 31);
+                mx = max(mx, (r << prm.tshift) | t);
+            }
+            if (lane < n && (mx >> prm.tshift) < (best >> prm.tshift)) best = mx;     // ties keep the lower composite
+        }
+        // ---- 4. stop iteration from the lane-0 promotions (reference :598-607)
+        const uint32_t K = best >> prm.tshift;
+        const bool is0 = lane < n && (best & tmask) == 0u;
+        const unsigned m0 = __ballot_sync(full, is0);
+        const int cnt0 = __popc(m0);
+        const long long limit = (long long)n * S * T;
+        long long stop = limit - 1;
+        if (cnt0 >= prm.knn) {
+            const bool need_c = prm.max_cand > prm.knn && cnt0 >= prm.max_cand;
+            int lt = 0, le = 0;                   // lane-0 promotions before / not after this lane's
+            for (int j = 0; j < 32; ++j) {
+                const uint32_t kj = __shfl_sync(full, K, j);
+                if ((m0 >> j) & 1u) { lt += kj < K ? 1 : 0; le += kj <= K ? 1 : 0; }
+            }
+            const unsigned ma = __ballot_sync(full, is0 && lt < prm.knn && prm.knn <= le);
+            const long long a = (long long)__shfl_sync(full, K, __ffs(ma) - 1);
+            const long long bcap = max(a, prm.outer_s - 1);
+            long long ccap;
+            if (prm.max_cand <= prm.knn) ccap = a;
+            else if (need_c) {
+                const unsigned mc = __ballot_sync(full, is0 && lt < prm.max_cand && prm.max_cand <= le);
+                ccap = max(a, (long long)__shfl_sync(full, K, __ffs(mc) - 1));
+            } else ccap = limit;
+            stop = min(min(bcap, ccap), limit - 1);
+        }
+        const uint32_t stop_enc = stop >= (long long)(0xFFFFFFFFu >> prm.tshift) ? 0xFFFFFFFFu
+                                                                                 : (((uint32_t)stop + 1u) << prm.tshift) - 1u;
+        const bool cand = lane < n && best <= stop_enc;
+        if (prm.work_stats) {                     // L <= 2 here (see the launch)
+            const int ncand = __popc(__ballot_sync(full, cand));
+            const int lane0 = __popc(__ballot_sync(full, is0 && (long long)K <= stop));
+            int entries = 0;
+            long long visits = 0;
+            for (int m = 0; m < L && m < 2; ++m) {
+                const uint32_t rkm = m ? rank_b : rank_a;
+                int e = (rkm != 0xFFFFFFFFu && (long long)rkm <= stop) ? (m ? span_b : span_a) : 0;
+                const int wm = __popc(__ballot_sync(full, rkm != 0xFFFFFFFFu));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) e += __shfl_xor_sync(full, e, o);
+                entries += e;
+                visits += min((long long)wm, stop + 1);
+            }
+            if (lane == 0) {
+                long long *st = prm.work_stats + ((size_t)q * prm.P + b) * 6;
+                const bool exhausted = stop > (long long)maxW;
+                st[0] = exhausted ? (long long)maxW : stop;
+                st[1] = visits; st[2] = entries; st[3] = ncand; st[4] = lane0; st[5] = exhausted ? 1 : 0;
+            }
+        }
+        // ---- 5. distances of the promoted points, the partition's top-k by a sort across the lanes
+        float bound_d = __int_as_float(0x7F800000), bound_sq = bound_d;
+        if (prm.qbound) {
+            const uint32_t bb = *reinterpret_cast<volatile uint32_t *>(prm.qbound + ql);
+            if (bb < 0x7F7F7F7Fu) {
+                bound_d = __uint_as_float(bb);
+                const float up = __uint_as_float(bb + 1u);
+                bound_sq = __fmul_ru(up, up);
+            }
+        }
+        uint64_t key = kEmptySlot;
+        if (cand) {
+            const long long gid = lo + lane;
+            const float *row = prm.data + (size_t)gid * dim, *qv = prm.query + (size_t)q * dim;
+            const float d = prm.vec8 ? dist_sequential_v8(row, qv, dim, bound_sq) : dist_sequential(row, qv, dim, prm.vec4);
+            if (d >= 0.0f && d <= bound_d) key = ((uint64_t)__float_as_uint(d) << 32) | (uint32_t)gid;
+        }
+#pragma unroll
+        for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                const uint64_t other = __shfl_xor_sync(full, key, stride);
+                const bool up = (lane & size) == 0, low = (lane & stride) == 0;
+                key = (low == up) ? min(key, other) : max(key, other);
+            }
+        }
+        uint64_t *out = prm.part_topk + ((size_t)ql * prm.num_parts + b) * prm.kpart;
+        if (lane < prm.kpart) out[lane] = key;
+        if (prm.qbound && prm.kpart == prm.knn) {
+            const uint64_t kth = __shfl_sync(full, key, prm.knn - 1);
+            if (lane == 0 && kth != kEmptySlot) atomicMin(prm.qbound + ql, (uint32_t)(kth >> 32));
+        }
+    }
+}
+
+}  // namespace dci
