@@ -20,13 +20,18 @@
 
 namespace dci {
 
+// nbuckets > 0: room for the counting rank (bucket counters over the radix histogram's place, one
+// arrival byte per key); 0: radix sort only.
 template <typename ValT>
 struct BuildLayout {
-    size_t hist_bytes, buf_bytes;
+    size_t hist_bytes, slot_bytes, buf_bytes;
     __host__ __device__ static size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
-    __host__ __device__ static BuildLayout make(int nthreads, int cap) {
+    __host__ __device__ static BuildLayout make(int nthreads, int cap, int nbuckets) {
         BuildLayout l;
-        l.hist_bytes = align16((size_t)256 * (nthreads / 32) * sizeof(ValT));
+        const size_t radix = (size_t)256 * (nthreads / 32) * sizeof(ValT);
+        const size_t counters = nbuckets > 0 ? (size_t)(nbuckets + 16) * sizeof(ValT) : 0;
+        l.hist_bytes = align16(radix > counters ? radix : counters);
+        l.slot_bytes = nbuckets > 0 ? align16((size_t)cap) : 0;
         l.buf_bytes = align16((size_t)cap * 4) * 2 + align16((size_t)cap * sizeof(ValT)) * 2;
         return l;
     }
@@ -40,12 +45,14 @@ __global__ void __launch_bounds__(1024)
 build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_indices, int ppb,
                       int num_parts, float *__restrict__ skeys, int *__restrict__ sids,
                       ValT *__restrict__ spos, float *__restrict__ skeysT, int T,
-                      unsigned char *gscratch, size_t gscratch_per_cta) {
+                      unsigned char *gscratch, size_t gscratch_per_cta, int nbuckets) {
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     __shared__ uint32_t warp_tot[40];
-    const BuildLayout<ValT> lay = BuildLayout<ValT>::make(blockDim.x, ppb);
+    __shared__ uint32_t s_lohi[2];
+    const BuildLayout<ValT> lay = BuildLayout<ValT>::make(blockDim.x, ppb, SMEM ? nbuckets : 0);
     ValT *hist = reinterpret_cast<ValT *>(dyn_smem);
-    unsigned char *big = SMEM ? dyn_smem + lay.hist_bytes : gscratch + (size_t)blockIdx.x * gscratch_per_cta;
+    uint8_t *slot = reinterpret_cast<uint8_t *>(dyn_smem + lay.hist_bytes);
+    unsigned char *big = SMEM ? dyn_smem + lay.hist_bytes + lay.slot_bytes : gscratch + (size_t)blockIdx.x * gscratch_per_cta;
     const size_t kbytes = BuildLayout<ValT>::align16((size_t)ppb * 4);
     const size_t vbytes = BuildLayout<ValT>::align16((size_t)ppb * sizeof(ValT));
     uint32_t *kA = reinterpret_cast<uint32_t *>(big);
@@ -60,19 +67,69 @@ build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_in
         const size_t row = segment_start(lo, i, num_indices, n);
         const size_t urow = (size_t)i * N + lo;               // the projection writes [I][N]
         const size_t prow = pos_segment_start(b, i, num_indices, ppb);
+        uint32_t kmin = 0xFFFFFFFFu, kmax = 0u;
         for (int x = threadIdx.x; x < n; x += blockDim.x) {
-            kA[x] = float_to_ordered(keys_unsorted[urow + x]);
-            vA[x] = (ValT)x;
+            const uint32_t k = float_to_ordered(keys_unsorted[urow + x]);
+            kA[x] = k;
+            kmin = min(kmin, k); kmax = max(kmax, k);
         }
-        __syncthreads();
-        cta_radix_sort<ValT, ValT, false>(kA, vA, kB, vB, n, hist, warp_tot, (ValT *)nullptr);
+        const uint32_t *ks = kA;          // the sorted keys and the points they belong to, once sorted
+        const ValT *vs = vA;
+        bool ranked = false;
+        if (SMEM && nbuckets > 0) {
+            // Counting rank: the keys are dropped into equal-width value buckets between the segment's
+            // smallest and largest key (about two buckets per key), a scan gives the bucket starts, and a
+            // key's place is its bucket's start plus the number of smaller keys (ties by point id) among
+            // its few bucket mates.  One pass over the keys each instead of the radix sort's eight.
+            if (threadIdx.x == 0) { s_lohi[0] = 0xFFFFFFFFu; s_lohi[1] = 0u; }
+            cta_zero16(hist, lay.hist_bytes);
+            __syncthreads();
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                kmin = min(kmin, __shfl_xor_sync(0xFFFFFFFFu, kmin, o));
+                kmax = max(kmax, __shfl_xor_sync(0xFFFFFFFFu, kmax, o));
+            }
+            if ((threadIdx.x & 31) == 0) { atomicMin(&s_lohi[0], kmin); atomicMax(&s_lohi[1], kmax); }
+            __syncthreads();
+            const float fmin_ = ordered_to_float(s_lohi[0]), range = ordered_to_float(s_lohi[1]) - fmin_;
+            const bool usable = range > 0.0f && range < 3.0e38f;
+            const float scale = usable ? (float)nbuckets / range : 0.0f;
+            const int last = nbuckets - 1;
+            auto bucket = [fmin_, scale, last](uint32_t k) {
+                return bucket_of(__float_as_uint(ordered_to_float(k) - fmin_), scale, last);
+            };
+            int over = usable ? 0 : 1;
+            if (usable)
+                for (int x = threadIdx.x; x < n; x += blockDim.x)
+                    slot[x] = (uint8_t)min(bucket_arrive(hist, bucket(kA[x])), 255u);
+            __syncthreads();
+            for (int j = threadIdx.x; j < nbuckets; j += blockDim.x) over |= ((uint32_t)hist[j] > (uint32_t)kMaxBucket);
+            over = __syncthreads_or(over);
+            if (!over) {
+                cta_bucket_place_and_rank<ValT, ValT>(kA, n, slot, vA, kB, hist, nbuckets, bucket, warp_tot, vB,
+                                                      [](uint32_t a, uint32_t b2) { return a < b2; }, [](int) {});
+                for (int x = threadIdx.x; x < n; x += blockDim.x) {       // vB[x] = place of point x
+                    const uint32_t r = vB[x];
+                    kB[r] = kA[x];
+                    vA[r] = (ValT)x;
+                }
+                __syncthreads();
+                ks = kB;
+                ranked = true;
+            }
+        }
+        if (!ranked) {                     // many equal keys (or no shared memory for the counters): radix sort
+            for (int x = threadIdx.x; x < n; x += blockDim.x) vA[x] = (ValT)x;
+            __syncthreads();
+            cta_radix_sort<ValT, ValT, false>(kA, vA, kB, vB, n, hist, warp_tot, (ValT *)nullptr);
+        }
         const int qn = n / T, rem = n % T;
         for (int x = threadIdx.x; x < n; x += blockDim.x) {
             const int r = x % T, j = x / T;
-            skeysT[row + r * qn + min(r, rem) + j] = ordered_to_float(kA[x]);
-            skeys[row + x] = ordered_to_float(kA[x]);
-            sids[row + x] = (int)(lo + vA[x]);
-            spos[prow + vA[x]] = (ValT)x;
+            skeysT[row + r * qn + min(r, rem) + j] = ordered_to_float(ks[x]);
+            skeys[row + x] = ordered_to_float(ks[x]);
+            sids[row + x] = (int)(lo + vs[x]);
+            spos[prow + vs[x]] = (ValT)x;
         }
         for (int x = n + threadIdx.x; x < pos_stride(ppb); x += blockDim.x) spos[prow + x] = (ValT)0;
         __syncthreads();

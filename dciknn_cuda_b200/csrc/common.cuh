@@ -253,18 +253,19 @@ __device__ __forceinline__ int bucket_of(uint32_t key_bits, float scale, int las
 // bucket mates it compares with lie next to its own entry; the only scattered
 // access left is the store of the rank.  Without it every key looks its bucket
 // mates up through bval.
-template <typename ValT, typename CntT, typename TieLess, typename Mark>
+// bucket(k): the bucket of key k, the same monotone map that produced cnt and slot.
+template <typename ValT, typename CntT, typename Bucket, typename TieLess, typename Mark>
 __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, int W, const uint8_t *slot,
                                                           ValT *bval, uint32_t *bkey, CntT *cnt, int nbuckets,
-                                                          float scale, uint32_t *scratch, ValT *rank_out,
+                                                          Bucket bucket, uint32_t *scratch, ValT *rank_out,
                                                           TieLess tie_less, Mark mark) {
-    const int tid = threadIdx.x, last = nbuckets - 1;
+    const int tid = threadIdx.x;
     cta_scan_counters(cnt, nbuckets + 1, scratch);           // cnt[b] = start of bucket b, cnt[nbuckets] = W
     mark(8);
     if (bkey) {
         for (int w = tid; w < W; w += blockDim.x) {
             const uint32_t k = key[w];
-            const uint32_t dest = (uint32_t)cnt[bucket_of(k, scale, last)] + (uint32_t)slot[w];
+            const uint32_t dest = (uint32_t)cnt[bucket(k)] + (uint32_t)slot[w];
             bval[dest] = (ValT)w;
             bkey[dest] = k;
         }
@@ -272,7 +273,7 @@ __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, i
         mark(9);
         for (int j = tid; j < W; j += blockDim.x) {
             const uint32_t k = bkey[j];
-            const int b = bucket_of(k, scale, last);
+            const int b = bucket(k);
             const uint32_t lo = cnt[b], hi = cnt[b + 1];
             uint32_t r = lo;
             for (uint32_t j2 = lo; j2 < hi; ++j2) {
@@ -286,12 +287,12 @@ __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, i
         return;
     }
     for (int w = tid; w < W; w += blockDim.x)
-        bval[(uint32_t)cnt[bucket_of(key[w], scale, last)] + (uint32_t)slot[w]] = (ValT)w;
+        bval[(uint32_t)cnt[bucket(key[w])] + (uint32_t)slot[w]] = (ValT)w;
     __syncthreads();
     mark(9);
     for (int w = tid; w < W; w += blockDim.x) {
         const uint32_t k = key[w];
-        const int b = bucket_of(k, scale, last);
+        const int b = bucket(k);
         const uint32_t lo = cnt[b], hi = cnt[b + 1];
         uint32_t r = lo;
         if (hi - lo > 1)                                 // alone in its bucket: the rank is the bucket start

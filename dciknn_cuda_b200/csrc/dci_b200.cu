@@ -223,22 +223,29 @@ template <typename ValT>
 int launch_build(dci_b200 *h, const float *d_unsorted, cudaStream_t st) {
     const int I = h->L * h->S;
     const int nthreads = h->ppb >= 4096 ? 1024 : (h->ppb >= 1024 ? 512 : 256);
-    const auto lay = dci::BuildLayout<ValT>::make(nthreads, h->ppb);
     const long long nseg = (long long)I * h->num_parts;
     cudaFuncAttributes fa;
     DCI_CUDA(cudaFuncGetAttributes(&fa, dci::build_segments_kernel<ValT, true>));
     // the opt-in limit covers static + dynamic shared memory, and the driver reserves 1 KB per CTA
     const size_t static_smem = fa.sharedSizeBytes + 1024;
-    const bool smem = lay.hist_bytes + lay.buf_bytes + static_smem <= h->smem_optin;
+    // buckets of the counting rank: two per key, one per key, or none (radix sort only), whichever fits
+    int nbuckets = 0;
+    auto lay = dci::BuildLayout<ValT>::make(nthreads, h->ppb, 0);
+    for (int nb : {2 * h->ppb, h->ppb}) {
+        if (nb < 64 || sizeof(ValT) != 2 || nb > 65535 * 2) continue;      // 16-bit packed counters only
+        const auto l2 = dci::BuildLayout<ValT>::make(nthreads, h->ppb, nb);
+        if (l2.hist_bytes + l2.slot_bytes + l2.buf_bytes + static_smem <= h->smem_optin) { nbuckets = nb; lay = l2; break; }
+    }
+    const bool smem = lay.hist_bytes + lay.slot_bytes + lay.buf_bytes + static_smem <= h->smem_optin;
     if (smem) {
         auto kern = dci::build_segments_kernel<ValT, true>;
-        const size_t dyn = lay.hist_bytes + lay.buf_bytes;
+        const size_t dyn = lay.hist_bytes + lay.slot_bytes + lay.buf_bytes;
         DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
         int per_sm = (int)std::max<size_t>(1, std::min<size_t>(h->smem_per_sm / (dyn + 1024), 2048 / nthreads));
         const unsigned grid = (unsigned)std::min<long long>(nseg, (long long)h->sm_count * per_sm);
         kern<<<grid, nthreads, dyn, st>>>(d_unsorted, h->num_points, I, h->ppb, h->num_parts,
                                           (float *)h->keys.p, (int *)h->ids.p, (ValT *)h->pos.p, (float *)h->keysT.p, h->T,
-                                          nullptr, 0);
+                                          nullptr, 0, nbuckets);
     } else {
         auto kern = dci::build_segments_kernel<ValT, false>;
         const unsigned grid = (unsigned)std::min<long long>(nseg, (long long)h->sm_count * (2048 / nthreads));
@@ -246,7 +253,7 @@ int launch_build(dci_b200 *h, const float *d_unsorted, cudaStream_t st) {
         kern<<<grid, nthreads, lay.hist_bytes, st>>>(d_unsorted, h->num_points, I, h->ppb, h->num_parts,
                                                      (float *)h->keys.p, (int *)h->ids.p, (ValT *)h->pos.p,
                                                      (float *)h->keysT.p, h->T,
-                                                     (unsigned char *)h->scratch.p, lay.buf_bytes);
+                                                     (unsigned char *)h->scratch.p, lay.buf_bytes, 0);
     }
     h->launches++;
     DCI_CUDA(cudaGetLastError());

@@ -499,7 +499,8 @@ traverse_kernel(const TraverseParams prm) {
                            window_visit_order((int)b2 - woff[ha], nlv[ha], spv[ha]);
                 };
                 auto mark = [&](int slot_) { DCI_PHASE_MARK(slot_) };
-                cta_bucket_place_and_rank<ValT, ValT>(kA, Wm, slot, bval, bkey, cnt, lay.nbuckets, scale, s_scratch,
+                auto bucket = [scale, last_bucket](uint32_t k) { return bucket_of(k, scale, last_bucket); };
+                cta_bucket_place_and_rank<ValT, ValT>(kA, Wm, slot, bval, bkey, cnt, lay.nbuckets, bucket, s_scratch,
                                                       rk, tie_less, mark);
             } else {
                 // many equal priorities: stable radix sort of the windows laid out in visiting order
@@ -617,6 +618,7 @@ traverse_kernel(const TraverseParams prm) {
         const int cnt0 = s_count[0];
         const long long limit = (long long)n * S * T;
         long long stop = limit - 1;
+        long long stop_rule = 0x7FFFFFFFFFFFFFFFll;      // iteration at which the stop test fires (statistics)
         if (cnt0 >= prm.knn) {
             const bool need_c = prm.max_cand > prm.knn && cnt0 >= prm.max_cand;
             int bits = 1;
@@ -631,7 +633,8 @@ traverse_kernel(const TraverseParams prm) {
             if (prm.max_cand <= prm.knn) ccap = a;
             else if (need_c) ccap = max(a, (long long)sel[1]);
             else ccap = limit;
-            stop = min(min(bcap, ccap), limit - 1);
+            stop_rule = min(bcap, ccap);
+            stop = min(stop_rule, limit - 1);
         }
         int lane0_stat = 0;
         if (prm.work_stats) {
@@ -684,7 +687,9 @@ traverse_kernel(const TraverseParams prm) {
             entries = cta_sum(entries, s_scratch);
             if (tid == 0) {
                 long long *st = prm.work_stats + ((size_t)q * prm.P + b) * 6;
-                const bool exhausted = stop > (long long)maxW;
+                // the reference's loop runs out of windows at iteration maxW unless its stop test or its
+                // iteration bound ends it first
+                const bool exhausted = stop_rule > (long long)maxW && (long long)maxW < limit;
                 st[0] = exhausted ? (long long)maxW : stop;
                 st[1] = visits; st[2] = entries; st[3] = ncand; st[4] = lane0_stat; st[5] = exhausted ? 1 : 0;
             }
@@ -1138,6 +1143,7 @@ traverse_small_kernel(const TraverseParams prm) {
         const int cnt0 = __popc(m0);
         const long long limit = (long long)n * S * T;
         long long stop = limit - 1;
+        long long stop_rule = 0x7FFFFFFFFFFFFFFFll;      // iteration at which the stop test fires (statistics)
         if (cnt0 >= prm.knn) {
             const bool need_c = prm.max_cand > prm.knn && cnt0 >= prm.max_cand;
             int lt = 0, le = 0;                   // lane-0 promotions before / not after this lane's
@@ -1154,7 +1160,8 @@ traverse_small_kernel(const TraverseParams prm) {
                 const unsigned mc = __ballot_sync(full, is0 && lt < prm.max_cand && prm.max_cand <= le);
                 ccap = max(a, (long long)__shfl_sync(full, K, __ffs(mc) - 1));
             } else ccap = limit;
-            stop = min(min(bcap, ccap), limit - 1);
+            stop_rule = min(bcap, ccap);
+            stop = min(stop_rule, limit - 1);
         }
         const uint32_t stop_enc = stop >= (long long)(0xFFFFFFFFu >> prm.tshift) ? 0xFFFFFFFFu
                                                                                  : (((uint32_t)stop + 1u) << prm.tshift) - 1u;
@@ -1175,7 +1182,7 @@ traverse_small_kernel(const TraverseParams prm) {
             }
             if (lane == 0) {
                 long long *st = prm.work_stats + ((size_t)q * prm.P + b) * 6;
-                const bool exhausted = stop > (long long)maxW;
+                const bool exhausted = stop_rule > (long long)maxW && (long long)maxW < limit;
                 st[0] = exhausted ? (long long)maxW : stop;
                 st[1] = visits; st[2] = entries; st[3] = ncand; st[4] = lane0; st[5] = exhausted ? 1 : 0;
             }
