@@ -204,15 +204,15 @@ int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cud
     timer.start();
     // fewest passes over the points, then the smallest accumulator count that achieves it
     if (I <= 8)
-        dci::project_exact_kernel<8><<<grid, dci::kProjPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
+        dci::project_exact_kernel<8><<<grid, dci::kProjThreads, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
     else if (I <= 12)
-        dci::project_exact_kernel<12><<<grid, dci::kProjPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
+        dci::project_exact_kernel<12><<<grid, dci::kProjThreads, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
     else if (I <= 20)
-        dci::project_exact_kernel<20><<<grid, dci::kProjPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
-    else if (I <= 30)
-        dci::project_exact_kernel<30><<<grid, dci::kProjPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
+        dci::project_exact_kernel<20><<<grid, dci::kProjThreads, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
+    else if (I <= 32)
+        dci::project_exact_kernel<32><<<grid, dci::kProjThreads, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
     else
-        dci::project_exact_kernel<40><<<grid, dci::kProjPoints, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
+        dci::project_exact_kernel<40><<<grid, dci::kProjThreads, 0, st>>>(d_x, n, h->dim, h->d_proj, I, d_out);
     timer.stop();
     h->launches++;
     DCI_CUDA(cudaGetLastError());
