@@ -273,7 +273,7 @@ int pick_buckets(dci_b200 *h, dci::TraverseParams &prm, int nthreads, size_t sta
                                                          prm.wcap, prm.ppb, nb, prm.vec4 && !prm.vec8, c == 0);
         if (lay.fixed_bytes + lay.big_bytes + static_smem <= h->smem_optin) { prm.bkey = c == 0 ? 1 : 0; return nb; }
     }
-    prm.bkey = 0;
+    prm.bkey = 1;      // the work arrays live in the CTA's global slab: room is no concern, sequential access matters more
     return std::min(std::max(prm.wcap / 2, 64), 16384);
 }
 

@@ -79,3 +79,24 @@ def test_full_size_exhaustive_quota_gives_exact_knn(full):
         want_ids[i], want_d[i] = cand[i][bi[0]], bd[0]
     assert np.array_equal(dists.cpu().numpy().view(np.uint32), want_d.view(np.uint32))
     assert (ids.cpu().numpy() == want_ids).mean() > 0.999      # id order can differ only at exact distance ties
+
+
+def test_full_size_tensor_core_projection_moves_few_results(full):
+    """Keys from the tcgen05 3xTF32 projection differ from the exact ones in their last bits, which can
+    move a point across a window boundary.  Measured on all 10 000 benchmark queries: 99.77 % of the
+    result rows identical, recall unchanged.  That is below the 99.9 % the parity bar asks for, which is
+    why the exact projection is the default; this test pins the measured level on 2 000 queries."""
+    cfg, g, data_h, query_h, data = full
+    from dciknn_cuda_b200 import DCI
+    q = query_h.cuda()
+    want, _ = g.query(q, cfg["k"], cfg["outer"], return_int_ids=True)
+    t = DCI(cfg["dim"], cfg["L"], cfg["S"], cfg["P"], cfg["T"], 0, proj=g.get_proj())
+    t.set_projection("tf32x3")
+    t.add(data)
+    got, _ = t.query(q, cfg["k"], cfg["outer"], return_int_ids=True)
+    same = (got == want).all(1).float().mean().item()
+    assert same >= 0.99, same
+    truth = torch.cdist(q[:500], data).topk(cfg["k"], largest=False).indices
+    rec = [(x[:500].long().unsqueeze(2) == truth.unsqueeze(1)).any(2).float().mean().item() for x in (want, got)]
+    assert abs(rec[0] - rec[1]) < 0.005, rec
+    t.free()

@@ -43,4 +43,4 @@ def test_query_with_tensor_core_keys():
             g.set_projection("exact")
         res[mode] = g.query(query, 10, return_int_ids=True)
     same = (res["exact"][0] == res["tf32x3"][0]).all(1).float().mean().item()
-    assert same >= 0.95, same
+    assert same >= 0.98, same        # 0.9977 of 10 000 queries at the benchmark's full size (tests/test_gpu_fullsize.py)
