@@ -300,8 +300,12 @@ int launch_traverse(dci_b200 *h, dci::TraverseParams prm, int nthreads, cudaStre
     const bool likely_exhaustive = (long long)prm.max_cand * prm.T * 2 > 3ll * prm.ppb && prm.outer_s >= prm.wcap;
     if (smem && prm.vec8 && !prm.topk_global && !prm.blind && likely_exhaustive) {
         prm.dense_cap = next_pow2(prm.kpart + nthreads / 4);
-        const size_t per_q = (size_t)prm.dense_cap * 16 + (size_t)prm.dim * 4 + 16;
-        prm.qbatch = (int)std::max<size_t>(1, std::min<size_t>(dci::kMaxQBatch, lay.big_bytes / per_q));
+        // per query a pair of selection buffers; for the group the query vectors, always kMaxQBatch slots
+        // per coordinate
+        const size_t per_q = (size_t)prm.dense_cap * 16 + 16, dq_bytes = (size_t)prm.dim * 4 * dci::kMaxQBatch;
+        prm.qbatch = lay.big_bytes > dq_bytes
+                         ? (int)std::max<size_t>(1, std::min<size_t>(dci::kMaxQBatch, (lay.big_bytes - dq_bytes) / per_q))
+                         : 1;
     }
     prm.topk_global_off = lay.fallback_bytes + (smem ? 0 : lay.big_bytes);
     const size_t per_cta = prm.topk_global_off + (prm.topk_global ? (size_t)prm.topk_cap * 16 : 0);

@@ -241,6 +241,23 @@ __device__ __forceinline__ float dist_sequential_v8(const float *__restrict__ ro
     return sq > bound_sq ? -1.0f : __fsqrt_rn(sq);
 }
 
+// Packed fp32 arithmetic of sm_100: two independent IEEE operations per instruction, so the
+// results are those of the scalar operations.
+__device__ __forceinline__ float2 sub2(const float2 a, const float2 b) {
+    unsigned long long r;
+    asm("sub.rn.f32x2 %0, %1, %2;"
+        : "=l"(r)
+        : "l"(*reinterpret_cast<const unsigned long long *>(&a)), "l"(*reinterpret_cast<const unsigned long long *>(&b)));
+    return *reinterpret_cast<float2 *>(&r);
+}
+__device__ __forceinline__ float2 fma2sq(const float2 d, const float2 acc) {      // d * d + acc
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %1, %2;"
+        : "=l"(r)
+        : "l"(*reinterpret_cast<const unsigned long long *>(&d)), "l"(*reinterpret_cast<const unsigned long long *>(&acc)));
+    return *reinterpret_cast<float2 *>(&r);
+}
+
 // Same distances for 32 rows at a time by one warp: lane r owns row r.  The
 // rows are read from global memory in 64-byte pieces, four lanes per piece so
 // that every 32-byte sector fetched is used in full, staged through a padded
@@ -764,64 +781,65 @@ traverse_kernel(const TraverseParams prm) {
       if (BATCH && ndense > 0) {
         if (prm.phase_cycles && tid == 0) t_last = clock64();
         const size_t tk_bytes = (size_t)prm.dense_cap * 16;                      // two halves of u64[dense_cap]
-        float *dq = reinterpret_cast<float *>(big + (size_t)Q * tk_bytes);       // Q query vectors
-        for (int t = 0; t < ndense; ++t) {
-            const float *src = prm.query + (size_t)(prm.q0 + s_dense[t]) * dim;
-            for (int c = tid; c < dim; c += blockDim.x) dq[(size_t)t * dim + c] = src[c];
-            if (tid == 0) {
-                s_slot[t].count = 0; s_slot[t].half = 0; s_slot[t].thresh = kEmptySlot;
-                float bd = __int_as_float(0x7F800000), bsq = bd;     // the query's bound, as in phase 5
-                if (prm.qbound) {
-                    const uint32_t bb = *reinterpret_cast<volatile uint32_t *>(prm.qbound + s_dense[t]);
-                    if (bb < 0x7F7F7F7Fu) {
-                        bd = __uint_as_float(bb);
-                        const float up = __uint_as_float(bb + 1u);
-                        bsq = __fmul_ru(up, up);
-                    }
+        // the query vectors coordinate-major, kMaxQBatch slots per coordinate: one 128-bit load brings
+        // one coordinate of four queries, i.e. two packed operands
+        float *dq = reinterpret_cast<float *>(big + (size_t)Q * tk_bytes);
+        for (int e = tid; e < dim * kMaxQBatch; e += blockDim.x) {
+            const int t = e % kMaxQBatch, c = e / kMaxQBatch;
+            dq[e] = t < ndense ? prm.query[(size_t)(prm.q0 + s_dense[t]) * dim + c] : 0.0f;
+        }
+        if (tid < ndense) {
+            const int t = tid;
+            s_slot[t].count = 0; s_slot[t].half = 0; s_slot[t].thresh = kEmptySlot;
+            float bd = __int_as_float(0x7F800000), bsq = bd;     // the query's bound, as in phase 5
+            if (prm.qbound) {
+                const uint32_t bb = *reinterpret_cast<volatile uint32_t *>(prm.qbound + s_dense[t]);
+                if (bb < 0x7F7F7F7Fu) {
+                    bd = __uint_as_float(bb);
+                    const float up = __uint_as_float(bb + 1u);
+                    bsq = __fmul_ru(up, up);
                 }
-                s_bd[t] = bd; s_bsq[t] = bsq;
             }
+            s_bd[t] = bd; s_bsq[t] = bsq;
         }
         __syncthreads();
         const int n8 = dim >> 3;
         for (int base = 0; base < n; base += blockDim.x) {
             const int r = base + tid;
             const bool live = r < n;
-            float sq[kMaxQBatch];
+            float2 sq2[kMaxQBatch / 2];          // the sums of queries 2j and 2j + 1, each in the reference's order
 #pragma unroll
-            for (int t = 0; t < kMaxQBatch; ++t) sq[t] = 0.0f;
+            for (int t = 0; t < kMaxQBatch / 2; ++t) sq2[t] = make_float2(0.0f, 0.0f);
             if (live) {
                 const float *row = prm.data + (size_t)(lo + r) * dim;
                 for (int c = 0; c < n8; ++c) {
                     if ((c & 3) == 0 && c) {     // every 32 coordinates: is the row still within some query's bound?
                         bool any = false;
 #pragma unroll
-                        for (int t = 0; t < kMaxQBatch; ++t) any |= (t < ndense && sq[t] <= s_bsq[t]);
+                        for (int t = 0; t < kMaxQBatch; ++t)
+                            any |= (t < ndense && ((t & 1) ? sq2[t >> 1].y : sq2[t >> 1].x) <= s_bsq[t]);
                         if (!any) break;
                     }
-                    float a0, a1, a2, a3, a4, a5, a6, a7;
-                    asm volatile("ld.global.nc.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                                 : "=f"(a0), "=f"(a1), "=f"(a2), "=f"(a3), "=f"(a4), "=f"(a5), "=f"(a6), "=f"(a7)
-                                 : "l"(row + c * 8));
+                    float a[8];
+                    ld_row8(row + c * 8, a);
+                    const float4 *qc = reinterpret_cast<const float4 *>(dq + (size_t)c * 8 * kMaxQBatch);
 #pragma unroll
-                    for (int t = 0; t < kMaxQBatch; ++t) {
-                        if (t < ndense && sq[t] <= s_bsq[t]) {   // a sum beyond the bound stays there
-                            const float4 b0 = *reinterpret_cast<const float4 *>(dq + (size_t)t * dim + c * 8);
-                            const float4 b1 = *reinterpret_cast<const float4 *>(dq + (size_t)t * dim + c * 8 + 4);
-                            float s_ = sq[t], d;
-                            d = __fsub_rn(a0, b0.x); s_ = __fmaf_rn(d, d, s_);
-                            d = __fsub_rn(a1, b0.y); s_ = __fmaf_rn(d, d, s_);
-                            d = __fsub_rn(a2, b0.z); s_ = __fmaf_rn(d, d, s_);
-                            d = __fsub_rn(a3, b0.w); s_ = __fmaf_rn(d, d, s_);
-                            d = __fsub_rn(a4, b1.x); s_ = __fmaf_rn(d, d, s_);
-                            d = __fsub_rn(a5, b1.y); s_ = __fmaf_rn(d, d, s_);
-                            d = __fsub_rn(a6, b1.z); s_ = __fmaf_rn(d, d, s_);
-                            d = __fsub_rn(a7, b1.w); s_ = __fmaf_rn(d, d, s_);
-                            sq[t] = s_;
+                    for (int e = 0; e < 8; ++e) {
+                        const float2 ab = make_float2(a[e], a[e]);
+#pragma unroll
+                        for (int h4 = 0; h4 < kMaxQBatch / 4; ++h4) {
+                            if (4 * h4 < ndense) {               // the same for every thread
+                                const float4 b = qc[e * (kMaxQBatch / 4) + h4];
+                                sq2[2 * h4] = fma2sq(sub2(ab, make_float2(b.x, b.y)), sq2[2 * h4]);
+                                if (4 * h4 + 2 < ndense) sq2[2 * h4 + 1] = fma2sq(sub2(ab, make_float2(b.z, b.w)), sq2[2 * h4 + 1]);
+                            }
                         }
                     }
                 }
             }
+            float sq[kMaxQBatch];
+#pragma unroll
+            for (int t = 0; t < kMaxQBatch; ++t) sq[t] = (t & 1) ? sq2[t >> 1].y : sq2[t >> 1].x;
             DCI_PHASE_MARK(5)
             // the keys of a round are offered a quarter of the CTA at a time, so that a selection
             // buffer only needs room for blockDim/4 appends
