@@ -428,16 +428,20 @@ static int check_partition_limits(dci_b200 *h, int ppb, int thread_size) {
     return 0;
 }
 
+// Positions within a partition are kept in 16 bits while a position plus the offset of the window grid
+// (below thread_size) still fits; the traversal relies on this bound.
+static inline bool pos16(int ppb, int thread_size) { return (long long)ppb + thread_size <= 65536; }
+
 // bytes of the position array: every (partition, simple index) segment padded to pos_stride(ppb)
-static size_t pos_bytes(int I, int num_parts, int ppb) {
-    return (size_t)I * num_parts * dci::pos_stride(ppb) * (ppb <= 65535 ? sizeof(uint16_t) : sizeof(uint32_t));
+static size_t pos_bytes(int I, int num_parts, int ppb, int thread_size) {
+    return (size_t)I * num_parts * dci::pos_stride(ppb) * (pos16(ppb, thread_size) ? sizeof(uint16_t) : sizeof(uint32_t));
 }
 
-static int ensure_index_buffers(dci_b200 *h, size_t n_entries, int ppb, int num_parts) {
+static int ensure_index_buffers(dci_b200 *h, size_t n_entries, int ppb, int num_parts, int thread_size) {
     DCI_CUDA(h->keys.ensure(n_entries * sizeof(float)));
     DCI_CUDA(h->ids.ensure(n_entries * sizeof(int)));
     DCI_CUDA(h->keysT.ensure(n_entries * sizeof(float)));
-    DCI_CUDA(h->pos.ensure(pos_bytes(h->L * h->S, num_parts, ppb)));
+    DCI_CUDA(h->pos.ensure(pos_bytes(h->L * h->S, num_parts, ppb, thread_size)));
     return 0;
 }
 
@@ -457,12 +461,12 @@ int dci_b200_add(dci_b200_t *h, const float *d_data, int num_points, int block_s
     const int num_parts = (num_points + ppb - 1) / ppb;
     if (int rc = check_partition_limits(h, ppb, thread_size)) return rc;
     const size_t n_entries = (size_t)I * num_points;
-    if (int rc = ensure_index_buffers(h, n_entries, ppb, num_parts)) return rc;
+    if (int rc = ensure_index_buffers(h, n_entries, ppb, num_parts, thread_size)) return rc;
     DCI_CUDA(h->tmp_keys.ensure(n_entries * sizeof(float)));
     h->num_points = num_points; h->P = block_size; h->T = thread_size; h->ppb = ppb; h->num_parts = num_parts;
     h->d_data = d_data;
     int rc = launch_project(h, d_data, num_points, (float *)h->tmp_keys.p, st);
-    if (!rc) rc = (ppb <= 65535) ? launch_build<uint16_t>(h, (const float *)h->tmp_keys.p, st)
+    if (!rc) rc = pos16(ppb, thread_size) ? launch_build<uint16_t>(h, (const float *)h->tmp_keys.p, st)
                                  : launch_build<uint32_t>(h, (const float *)h->tmp_keys.p, st);
     if (rc) { h->num_points = 0; h->d_data = nullptr; }
     return rc;
@@ -510,9 +514,9 @@ int dci_b200_append(dci_b200_t *h, const float *d_all_data, int num_points_total
     DCI_CUDA_OR_EMPTY(cudaStreamSynchronize(st));
 #undef DCI_CUDA_OR_EMPTY
     // 3. every segment again, for the partition bounds of the new point count
-    if (int rc = ensure_index_buffers(h, (size_t)I * n_new, ppb, num_parts)) { h->num_points = 0; h->d_data = nullptr; return rc; }
+    if (int rc = ensure_index_buffers(h, (size_t)I * n_new, ppb, num_parts, h->T)) { h->num_points = 0; h->d_data = nullptr; return rc; }
     h->num_points = n_new; h->ppb = ppb; h->num_parts = num_parts; h->d_data = d_all_data;
-    int rc = (ppb <= 65535) ? launch_build<uint16_t>(h, (const float *)h->tmp_keys.p, st)
+    int rc = pos16(ppb, h->T) ? launch_build<uint16_t>(h, (const float *)h->tmp_keys.p, st)
                             : launch_build<uint32_t>(h, (const float *)h->tmp_keys.p, st);
     if (rc) { h->num_points = 0; h->d_data = nullptr; }
     return rc;
@@ -543,7 +547,7 @@ int dci_b200_set_index(dci_b200_t *h, const float *d_data, int num_points, int b
     DCI_CUDA(h->keys.ensure(n_entries * sizeof(float)));
     DCI_CUDA(h->ids.ensure(n_entries * sizeof(int)));
     DCI_CUDA(h->keysT.ensure(n_entries * sizeof(float)));
-    DCI_CUDA(h->pos.ensure(pos_bytes(I, num_parts, ppb)));
+    DCI_CUDA(h->pos.ensure(pos_bytes(I, num_parts, ppb, thread_size)));
     DCI_CUDA(h->errflag.ensure(sizeof(int)));
     DCI_CUDA(cudaMemsetAsync(h->errflag.p, 0, sizeof(int), st));
     // the caller's arrays are [I][N]; the kernel checks them and writes the partition-major index
@@ -554,8 +558,8 @@ int dci_b200_set_index(dci_b200_t *h, const float *d_data, int num_points, int b
     const unsigned grid = (unsigned)std::min<long long>((long long)I * num_parts, (long long)h->sm_count * 8);
     // positions start as a sentinel (all ones, beyond any partition) so that the second kernel sees
     // every point that no entry of its segment names
-    DCI_CUDA(cudaMemsetAsync(h->pos.p, 0xFF, pos_bytes(I, num_parts, ppb), st));
-    if (ppb <= 65535) {
+    DCI_CUDA(cudaMemsetAsync(h->pos.p, 0xFF, pos_bytes(I, num_parts, ppb, thread_size), st));
+    if (pos16(ppb, thread_size)) {
         dci::derive_index_kernel<uint16_t><<<grid, 256, 0, st>>>(
             (const float *)h->tmp_keys.p, (const int *)h->scratch.p, num_points, I, ppb, num_parts, thread_size,
             (float *)h->keys.p, (int *)h->ids.p, (uint16_t *)h->pos.p, (float *)h->keysT.p, (int *)h->errflag.p);
@@ -668,7 +672,7 @@ static int query_impl(dci_b200_t *h, const float *d_query, int num_queries, int 
         // partitions of at most 32 points with at most 32 windows per composite index: one warp per
         // (query, partition) pair instead of one CTA (per-phase cycle counters exist only in the CTA
         // kernel, and the warp kernel keeps statistics for at most two composite indices)
-        const bool small = h->ppb <= 32 && prm.wcap <= 32 && h->S <= 32 && !blind && !prm.topk_global &&
+        const bool small = h->ppb <= 32 && prm.wcap <= 32 && h->S <= 32 && pos16(h->ppb, h->T) && !blind && !prm.topk_global &&
                            !(h->stats_on & 2) && (!(h->stats_on & 1) || h->L <= 2);
         if (small) {
             const long long nwork = (long long)prm.nq * prm.num_parts;
@@ -680,7 +684,7 @@ static int query_impl(dci_b200_t *h, const float *d_query, int num_queries, int 
             h->last_qbatch = 1;
             DCI_CUDA(cudaGetLastError());
             rc = 0;
-        } else if (prm.ppb <= 65535)
+        } else if (pos16(prm.ppb, h->T))
             rc = (prm.wcap <= 65535) ? launch_traverse<uint16_t, uint16_t>(h, prm, nthreads, st)
                                      : launch_traverse<uint32_t, uint16_t>(h, prm, nthreads, st);
         else
@@ -1308,7 +1312,7 @@ extern "C" int dci_b200_query_noalloc(dci_b200_t *h, const float *d_query, int n
     prm.topk_cap = next_pow2(prm.kpart + nthreads);
     unsigned char *rest = scratch + 256 + qproj_bytes;
     const size_t avail = (size_t)DCI_B200_NOALLOC_SCRATCH_BYTES - 256 - qproj_bytes;
-    if (prm.ppb <= 65535)
+    if (pos16(prm.ppb, h->T))
         return (prm.wcap <= 65535)
                    ? query_noalloc_impl<uint16_t, uint16_t>(h, prm, nthreads, rest, avail, num_queries, d_ids, d_dists, st)
                    : query_noalloc_impl<uint32_t, uint16_t>(h, prm, nthreads, rest, avail, num_queries, d_ids, d_dists, st);

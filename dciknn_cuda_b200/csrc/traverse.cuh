@@ -552,6 +552,68 @@ traverse_kernel(const TraverseParams prm) {
                 uint32_t best[2 * kPairs];
 #pragma unroll
                 for (int j = 0; j < 2 * kPairs; ++j) best[j] = 0xFFFFFFFFu;
+                // 16-bit ranks and positions with windows of several points: the running maximum keeps
+                // the rank in its high half and the relative position (below 65536: the host uses
+                // 16-bit positions only while ppb + T <= 65536) in its low half.  The windows of one
+                // composite index have distinct ranks, so the largest packed word is the largest
+                // rank, and the lane (position mod T) is worked out once per composite from the
+                // winner's position.  Two simple indices per trip: the loads of one are in flight
+                // while the other's ranks are looked up, without register moves.
+                constexpr bool kPacked = !BATCH && !kT1 && sizeof(PosT) == 2 && sizeof(ValT) == 2;   // (the query-group variants have no registers to spare)
+                if constexpr (kPacked) {
+                    unsigned livemask = 0;
+#pragma unroll
+                    for (int j = 0; j < kPairs; ++j) livemask |= (pt + j * pair_step < n) ? (1u << j) : 0u;
+                    for (int m = 0; m < L; ++m) {
+                        const uint16_t *rkm = reinterpret_cast<const uint16_t *>(rank) + (size_t)m * prm.wcap;
+                        const uint16_t *rp = reinterpret_cast<const uint16_t *>(spos) + pos_segment_start(b, m * S, I, prm.ppb) + pt;
+                        uint32_t mx[2 * kPairs];
+#pragma unroll
+                        for (int j = 0; j < 2 * kPairs; ++j) mx[j] = 0u;
+                        uint32_t wa[kPairs], wb[kPairs];
+#pragma unroll
+                        for (int j = 0; j < kPairs; ++j)
+                            wa[j] = ((livemask >> j) & 1u) ? __ldg(reinterpret_cast<const uint32_t *>(rp + j * pair_step)) : 0u;
+                        auto lookups = [&](const uint32_t (&pw)[kPairs], const int h) {
+                            const int2 cb = s_cb[m * S + h];
+                            const uint16_t *rkb = rkm + cb.y;
+                            const uint32_t c2 = (uint32_t)cb.x * 0x10001u;
+#pragma unroll
+                            for (int j = 0; j < kPairs; ++j) {
+                                const uint32_t w2 = pw[j] + c2;        // both positions made relative to window 0 at once
+#pragma unroll
+                                for (int e = 0; e < 2; ++e) {
+                                    const uint32_t x = e ? (w2 >> 16) : (w2 & 0xFFFFu);
+                                    const uint32_t g = __umulhi(x, prm.divT.magic);
+                                    mx[2 * j + e] = max(mx[2 * j + e], ((uint32_t)rkb[g] << 16) | x);
+                                }
+                            }
+                        };
+                        int h = 0;
+                        for (; h + 2 <= S; h += 2) {
+                            rp += pstride;
+#pragma unroll
+                            for (int j = 0; j < kPairs; ++j)
+                                wb[j] = ((livemask >> j) & 1u) ? __ldg(reinterpret_cast<const uint32_t *>(rp + j * pair_step)) : 0u;
+                            lookups(wa, h);
+                            if (h + 2 < S) {
+                                rp += pstride;
+#pragma unroll
+                                for (int j = 0; j < kPairs; ++j)
+                                    wa[j] = ((livemask >> j) & 1u) ? __ldg(reinterpret_cast<const uint32_t *>(rp + j * pair_step)) : 0u;
+                            }
+                            lookups(wb, h + 1);
+                        }
+                        if (h < S) lookups(wa, h);
+#pragma unroll
+                        for (int j = 0; j < 2 * kPairs; ++j) {
+                            if ((mx[j] >> 16) < (best[j] >> prm.tshift)) {     // ties keep the lower composite
+                                const uint32_t x = mx[j] & 0xFFFFu, g = __umulhi(x, prm.divT.magic);
+                                best[j] = (mx[j] >> 16) * tmul + (x - g * (uint32_t)T);
+                            }
+                        }
+                    }
+                } else {
                 for (int m = 0; m < L; ++m) {
                     const ValT *rkm = rank + (size_t)m * prm.wcap;
                     const PosT *row = spos + pos_segment_start(b, m * S, I, prm.ppb) + pt;
@@ -591,6 +653,7 @@ traverse_kernel(const TraverseParams prm) {
 #pragma unroll
                     for (int j = 0; j < 2 * kPairs; ++j)
                         if ((mx[j] >> prm.tshift) < (best[j] >> prm.tshift)) best[j] = mx[j];   // ties keep the lower composite
+                }
                 }
                 // one reservation per warp for the lane-0 promotions of all its points (every warp of
                 // the CTA appends to the same counter)
