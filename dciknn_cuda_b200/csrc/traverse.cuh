@@ -76,7 +76,7 @@ struct TraverseParams {
 };
 
 constexpr int kMaxQBatch = 8;                  // queries whose exhaustive distance phases share row loads
-constexpr int kPriWidth = 5;                   // simple indices whose window keys a thread loads together
+constexpr int kPriWidth = 5;                   // window keys a thread loads together in the priority pass
 constexpr int kDistChunk = 16;                 // floats of a row staged per step of the distance phase
 constexpr int kDistStride = kDistChunk + 4;    // padded row stride of the staging tile (floats)
 
@@ -469,39 +469,51 @@ traverse_kernel(const TraverseParams prm) {
             cta_zero16(cnt, lay.cnt_bytes);
             __syncthreads();
             DCI_PHASE_MARK(10)
-            const int gmax = prm.wcap / S;                  // no simple index has more windows than this
             const int last_t = ((n - 1) % T) * (n / T) + min((n - 1) % T, n % T) + (n - 1) / T;
-            for (int h0 = 0; h0 < S; h0 += kPriWidth) {
-                for (int g = tid; g < gmax; g += blockDim.x) {
-                    float kv[kPriWidth];
+            // The threads are split among the simple indices, so that a thread keeps one index's
+            // constants in registers and walks that index's windows, kPriWidth key loads in flight.
+            // A bucket that grows beyond kMaxBucket is noticed by the arrival that exceeds it.
+            int over = buckets_ok ? 0 : 1;
+            {
+                const int tpi = max(1, (int)blockDim.x / S), slots = (int)blockDim.x / tpi;
+                const int sl = tid / tpi, r = tid - sl * tpi;
+                if (sl < slots)
+                for (int h = sl; h < S; h += slots) {
+                    const int i = m * S + h;
+                    const int cnt_i = s_cnt[i], c = s_cb[i].x, kt = s_kt[i], wbase = woff[h];
+                    const float qp = s_qp[i];
+                    const float *kT = prm.skeysT + segment_start(lo, i, I, n);
+                    for (int g0 = r; g0 < cnt_i; g0 += tpi * kPriWidth) {
+                        float kv[kPriWidth];
 #pragma unroll
-                    for (int u = 0; u < kPriWidth; ++u) {
-                        const int i = m * S + h0 + u;
-                        kv[u] = 0.0f;
-                        if (h0 + u < S && g < s_cnt[i]) {
-                            // window starts are contiguous in the stride-T layout; the two clamped
-                            // cases read the segment's first / last key
-                            const int start = g * T - s_cb[i].x;
-                            const int at = start < 0 ? 0 : (start >= n ? last_t : s_kt[i] + g);
-                            kv[u] = __ldg(prm.skeysT + segment_start(lo, i, I, n) + at);
+                        for (int u = 0; u < kPriWidth; ++u) {
+                            const int g = g0 + u * tpi;
+                            kv[u] = 0.0f;
+                            if (g < cnt_i) {
+                                // window starts are contiguous in the stride-T layout; the two clamped
+                                // cases read the segment's first / last key
+                                const int start = g * T - c;
+                                const int at = start < 0 ? 0 : (start >= n ? last_t : kt + g);
+                                kv[u] = __ldg(kT + at);
+                            }
                         }
-                    }
 #pragma unroll
-                    for (int u = 0; u < kPriWidth; ++u) {
-                        const int i = m * S + h0 + u;
-                        if (h0 + u < S && g < s_cnt[i]) {
-                            const uint32_t bits = __float_as_uint(fabsf(kv[u] - s_qp[i]));
-                            const int w = woff[h0 + u] + g;
-                            kA[w] = bits;
-                            if (buckets_ok)
-                                slot[w] = (uint8_t)min(bucket_arrive(cnt, bucket_of(bits, scale, last_bucket)), 255u);
+                        for (int u = 0; u < kPriWidth; ++u) {
+                            const int g = g0 + u * tpi;
+                            if (g < cnt_i) {
+                                const uint32_t bits = __float_as_uint(fabsf(kv[u] - qp));
+                                const int w = wbase + g;
+                                kA[w] = bits;
+                                if (buckets_ok) {
+                                    const uint32_t arrival = bucket_arrive(cnt, bucket_of(bits, scale, last_bucket));
+                                    over |= (arrival >= (uint32_t)kMaxBucket);
+                                    slot[w] = (uint8_t)min(arrival, 255u);
+                                }
+                            }
                         }
                     }
                 }
             }
-            int over = buckets_ok ? 0 : 1;
-            __syncthreads();
-            for (int i = tid; i < lay.nbuckets; i += blockDim.x) over |= ((uint32_t)cnt[i] > (uint32_t)kMaxBucket);
             over = __syncthreads_or(over);
             DCI_PHASE_MARK(1)
             ValT *rk = rank + (size_t)m * prm.wcap;
