@@ -94,8 +94,8 @@ __device__ __forceinline__ void cta_exclusive_scan_u16x8(uint16_t *a, int n, uin
     uint32_t sum = 0;
     for (int g = g0; g < g1; ++g) {
         const uint4 x = v[g];
-        sum += (x.x & 0xFFFFu) + (x.x >> 16) + (x.y & 0xFFFFu) + (x.y >> 16) + (x.z & 0xFFFFu) + (x.z >> 16) +
-               (x.w & 0xFFFFu) + (x.w >> 16);
+        const uint32_t s2 = x.x + x.y + x.z + x.w;     // low and high halves summed side by side: no carry, the total stays below 65 536
+        sum += (s2 & 0xFFFFu) + (s2 >> 16);
     }
     uint32_t inc = sum;
 #pragma unroll
@@ -120,11 +120,11 @@ __device__ __forceinline__ void cta_exclusive_scan_u16x8(uint16_t *a, int n, uin
     for (int g = g0; g < g1; ++g) {
         const uint4 x = v[g];
         uint4 y;
-        uint32_t c;
-        c = x.x & 0xFFFFu; y.x = base; base += c; c = x.x >> 16; y.x |= base << 16; base += c;
-        c = x.y & 0xFFFFu; y.y = base; base += c; c = x.y >> 16; y.y |= base << 16; base += c;
-        c = x.z & 0xFFFFu; y.z = base; base += c; c = x.z >> 16; y.z |= base << 16; base += c;
-        c = x.w & 0xFFFFu; y.w = base; base += c; c = x.w >> 16; y.w |= base << 16; base += c;
+        // exclusive prefix of the pair (lo, hi) from base: low half base, high half base + lo
+        y.x = base * 0x10001u + (x.x << 16); base += (x.x & 0xFFFFu) + (x.x >> 16);
+        y.y = base * 0x10001u + (x.y << 16); base += (x.y & 0xFFFFu) + (x.y >> 16);
+        y.z = base * 0x10001u + (x.z << 16); base += (x.z & 0xFFFFu) + (x.z >> 16);
+        y.w = base * 0x10001u + (x.w << 16); base += (x.w & 0xFFFFu) + (x.w >> 16);
         v[g] = y;
     }
     __syncthreads();
@@ -271,17 +271,32 @@ __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, i
         }
         __syncthreads();
         mark(9);
+        // The first kRankBatch mates of the bucket are compared without a branch (most buckets hold
+        // no more), the rest one by one; equal keys are only counted there and settled by tie_less
+        // in a loop of their own, which few entries enter.  A slot beyond the bucket reads as the
+        // largest key: never smaller, and equal only to a key that takes the tie loop anyway.
+        constexpr int kRankBatch = 4;
         for (int j = tid; j < W; j += blockDim.x) {
             const uint32_t k = bkey[j];
             const int b = bucket(k);
             const uint32_t lo = cnt[b], hi = cnt[b + 1];
-            uint32_t r = lo;
-            for (uint32_t j2 = lo; j2 < hi; ++j2) {
+            const uint32_t me = (uint32_t)bval[j];
+            uint32_t r = lo, ties = 0;
+            uint32_t kk[kRankBatch];
+#pragma unroll
+            for (int u = 0; u < kRankBatch; ++u) kk[u] = (lo + u < hi) ? bkey[lo + u] : 0xFFFFFFFFu;
+#pragma unroll
+            for (int u = 0; u < kRankBatch; ++u) { r += (kk[u] < k); ties += (kk[u] == k); }
+            for (uint32_t j2 = lo + kRankBatch; j2 < hi; ++j2) {
                 const uint32_t k2 = bkey[j2];
-                if (k2 < k) ++r;
-                else if (k2 == k && j2 != (uint32_t)j && tie_less((uint32_t)bval[j2], (uint32_t)bval[j])) ++r;
+                r += (k2 < k);
+                ties += (k2 == k);
             }
-            rank_out[bval[j]] = (ValT)r;
+            if (ties > 1) {                                  // the entry itself is one of them
+                for (uint32_t j2 = lo; j2 < hi; ++j2)
+                    if (bkey[j2] == k && j2 != (uint32_t)j && tie_less((uint32_t)bval[j2], me)) ++r;
+            }
+            rank_out[me] = (ValT)r;
         }
         __syncthreads();
         return;
