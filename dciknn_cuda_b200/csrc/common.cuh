@@ -231,6 +231,7 @@ __device__ void cta_radix_sort(uint32_t *kA, ValT *vA, uint32_t *kB, ValT *vB, i
 }
 
 constexpr int kMaxBucket = 48;   // largest bucket the counting rank accepts
+constexpr int kRankBatch = 4;    // bucket mates compared without a branch
 
 // Bucket of a non-negative fp32 key: equal-width value buckets, a monotone map.  key * scale is
 // rounded to an integer by adding 2^23 (the sum's low mantissa bits are then that integer): one
@@ -275,7 +276,6 @@ __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, i
         // no more), the rest one by one; equal keys are only counted there and settled by tie_less
         // in a loop of their own, which few entries enter.  A slot beyond the bucket reads as the
         // largest key: never smaller, and equal only to a key that takes the tie loop anyway.
-        constexpr int kRankBatch = 4;
         for (int j = tid; j < W; j += blockDim.x) {
             const uint32_t k = bkey[j];
             const int b = bucket(k);
@@ -309,18 +309,25 @@ __device__ __forceinline__ void cta_bucket_place_and_rank(const uint32_t *key, i
         const uint32_t k = key[w];
         const int b = bucket(k);
         const uint32_t lo = cnt[b], hi = cnt[b + 1];
-        uint32_t r = lo;
-        if (hi - lo > 1)                                 // alone in its bucket: the rank is the bucket start
-        for (uint32_t j0 = lo; j0 < hi; j0 += 4) {      // four bucket mates at a time: independent loads
-            uint32_t other[4], kj[4];
+        uint32_t r = lo, ties = 0;
+        {                                                // the first four mates without a branch, as above
+            uint32_t other[kRankBatch], kj[kRankBatch];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) other[u] = j0 + u < hi ? (uint32_t)bval[j0 + u] : (uint32_t)w;
+            for (int u = 0; u < kRankBatch; ++u) other[u] = lo + u < hi ? (uint32_t)bval[lo + u] : (uint32_t)w;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) kj[u] = key[other[u]];
+            for (int u = 0; u < kRankBatch; ++u) kj[u] = lo + u < hi ? key[other[u]] : 0xFFFFFFFFu;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
-                if (kj[u] < k) ++r;
-                else if (kj[u] == k && other[u] != (uint32_t)w && tie_less(other[u], (uint32_t)w)) ++r;
+            for (int u = 0; u < kRankBatch; ++u) { r += (kj[u] < k); ties += (kj[u] == k); }
+        }
+        for (uint32_t j2 = lo + kRankBatch; j2 < hi; ++j2) {
+            const uint32_t k2 = key[bval[j2]];
+            r += (k2 < k);
+            ties += (k2 == k);
+        }
+        if (ties > 1) {
+            for (uint32_t j2 = lo; j2 < hi; ++j2) {
+                const uint32_t o = (uint32_t)bval[j2];
+                if (o != (uint32_t)w && key[o] == k && tie_less(o, (uint32_t)w)) ++r;
             }
         }
         rank_out[w] = (ValT)r;

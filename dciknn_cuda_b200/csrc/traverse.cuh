@@ -554,12 +554,13 @@ traverse_kernel(const TraverseParams prm) {
         // and the loads of the next index are in flight while this one's ranks are looked up.
         const uint32_t tmul = 1u << prm.tshift;
         // one pass: this thread's kPairs pairs, pair j = points p0 + 2 * (j * blockDim + tid) and the next one
-        auto promote_pass = [&](auto t_is_one, auto pairs_tag, const int p0) {
+        // `pair_step` is twice the number of threads that take part (a multiple of 32); the others sit
+        // the pass out, whole warps at a time.
+        auto promote_pass = [&](auto t_is_one, auto pairs_tag, const int p0, const int pair_step) {
             constexpr bool kT1 = decltype(t_is_one)::value;
             constexpr int kPairs = decltype(pairs_tag)::value;
             const size_t pstride = (size_t)pos_stride(prm.ppb);
-            const int pair_step = 2 * (int)blockDim.x;
-            {
+            if (2 * tid < pair_step) {
                 const int pt = p0 + 2 * tid;                       // first point of this thread's pair 0
                 uint32_t best[2 * kPairs];
 #pragma unroll
@@ -698,8 +699,13 @@ traverse_kernel(const TraverseParams prm) {
                 const int units = (n - p0 + pair_step - 1) / pair_step;
                 // pairs of the large pass; none where the registers are needed elsewhere (query groups)
                 constexpr int kBig = BATCH ? 0 : (sizeof(PosT) != 2 ? 2 : (SMEM ? 5 : 4));
-                if (kBig > 1 && units >= kBig - 1) { promote_pass(t_is_one, IntTag<(kBig > 1 ? kBig : 1)>{}, p0); p0 += kBig * pair_step; }
-                else { promote_pass(t_is_one, IntTag<1>{}, p0); p0 += pair_step; }
+                if (kBig > 1 && units >= 2) {
+                    // a full pass, or for a short rest the same pass by as many warps as it takes
+                    int step = pair_step;
+                    if (units < kBig - 1) step = 2 * ((((n - p0 + 1) / 2 + kBig - 1) / max(kBig, 1) + 31) & ~31);
+                    promote_pass(t_is_one, IntTag<(kBig > 1 ? kBig : 1)>{}, p0, step);
+                    p0 += kBig * step;
+                } else { promote_pass(t_is_one, IntTag<1>{}, p0, pair_step); p0 += pair_step; }
             }
         };
         if (T == 1) promote(TrueTag{}); else promote(FalseTag{});
