@@ -389,11 +389,12 @@ class DCI(object):
         return out
 
     def set_projection(self, mode):
-        """'exact' (default; fixed fp32 summation order), 'tf32x3' (tcgen05 tensor cores, persistent
-        TMA pipeline when the shapes allow), 'tf32x3_plain' (tensor cores, plain loads) or
-        'tf32x3_tile' (tensor cores, one TMA-fed tile per CTA)."""
+        """'exact' (default; fixed fp32 summation order, rows streamed by TMA when the shapes allow),
+        'exact_plain' (the same keys bit for bit, rows always staged by the computing threads),
+        'tf32x3' (tcgen05 tensor cores, persistent TMA pipeline when the shapes allow), 'tf32x3_plain'
+        (tensor cores, plain loads) or 'tf32x3_tile' (tensor cores, one TMA-fed tile per CTA)."""
         rc = _capi.lib().dci_b200_set_projection(
-            self._live(), {"exact": 0, "tf32x3": 1, "tf32x3_plain": 2, "tf32x3_tile": 3}[mode])
+            self._live(), {"exact": 0, "tf32x3": 1, "tf32x3_plain": 2, "tf32x3_tile": 3, "exact_plain": 4}[mode])
         if rc == _capi.ERR_STATE:
             raise RuntimeError(_capi.lib().dci_b200_last_error().decode())
         _capi.check(rc)

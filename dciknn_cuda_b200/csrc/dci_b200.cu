@@ -22,6 +22,7 @@
 #include "directions.cuh"
 #include "project.cuh"
 #include "project_tf32.cuh"
+#include "project_exact_tma.cuh"
 #include "traverse.cuh"
 
 namespace {
@@ -93,18 +94,19 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// Tensor map over a row-major fp32 matrix [rows][dim] with boxes of [box_rows][32 columns] and the
-// 128-byte swizzle; out-of-range elements read as zero.
-bool make_tensor_map_2d(CUtensorMap *map, const float *ptr, long long rows, int dim, int box_rows) {
+// Tensor map over a row-major fp32 matrix [rows][dim] with boxes of [box_rows][box_cols = 32 or 16] and
+// the swizzle of that row width; out-of-range elements read as zero.
+bool make_tensor_map_2d(CUtensorMap *map, const float *ptr, long long rows, int dim, int box_rows, int box_cols = 32) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn || dim % 4 != 0 || ((uintptr_t)ptr & 15) != 0 || box_rows < 1 || box_rows > 256 || rows < 1) return false;
     const cuuint64_t dims[2] = {(cuuint64_t)dim, (cuuint64_t)rows};
     const cuuint64_t strides[1] = {(cuuint64_t)dim * sizeof(float)};
-    const cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};
+    const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1u, 1u};
+    // the swizzle spans a box row: 128 bytes for 32 columns, 64 bytes for 16
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)ptr, dims, strides, box, estr,
-              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+              CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 16 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace
@@ -114,6 +116,8 @@ struct dci_b200 {
     int num_points = 0, P = 0, T = 0, ppb = 0, num_parts = 0;
     const float *d_data = nullptr;       // borrowed
     float *d_proj = nullptr;             // [L*S][dim]
+    int *d_copyflag = nullptr;           // set (and left set) by a TMA-fed kernel whose bounded wait ran out
+    int exact_tma = 1;                   // 0: never use the TMA-fed exact projection
     Buf keys, ids, pos, keysT;           // sorted index, inverse positions, stride-T keys: L*S*N entries each, partition-major (segment_start)
     int max_ctas = 0;                    // > 0: cap on the traversal grid (dci_b200_set_max_ctas)
     Buf tmp_keys, qproj, part_topk, scratch, merge_scratch, stats, phases, hq, hids, hdists, qbound;
@@ -200,6 +204,43 @@ int launch_project(dci_b200 *h, const float *d_x, long long n, float *d_out, cud
         if (flag) return fail(DCI_B200_ERR_CUDA, "tensor-core projection: a wait on the MMA barrier timed out");
         return 0;
     }
+    // Large inputs take the TMA-fed kernel when the rows can be described by a tensor map (dim a multiple
+    // of 4, 16-byte aligned base), one pass covers all directions and they fit in shared memory beside at
+    // least two stages; everything else takes the kernel that stages the rows itself.  Same arithmetic.
+    if (h->exact_tma && I <= 40 && n >= 1024) {
+        const int dirs = I <= 8 ? 8 : (I <= 12 ? 12 : (I <= 20 ? 20 : (I <= 32 ? 32 : 40)));
+        const size_t dbytes = dci::px_dirs_bytes(h->dim, dirs);
+        const long long stage = dci::px_stage_bytes(dirs);
+        const long long per_cta2 = (long long)h->smem_per_sm / 2 - 1024 - 1024 - 512 - (long long)dbytes;   // two CTAs per SM
+        const long long per_cta1 = (long long)h->smem_optin - 1024 - 512 - (long long)dbytes;
+        int stages = 0, per_sm = 0;
+        if (per_cta2 >= 3 * stage) { stages = (int)std::min<long long>(4, per_cta2 / stage); per_sm = 2; }
+        else if (per_cta1 >= 2 * stage) { stages = (int)std::min<long long>(dci::kPxMaxStages, per_cta1 / stage); per_sm = 1; }
+        CUtensorMap map_x;
+        if (stages && make_tensor_map_2d(&map_x, d_x, n, h->dim, dci::kPxBoxRows, dci::kPxCols)) {
+            const size_t dyn = dci::px_smem_bytes(h->dim, dirs, stages);
+            const long long ntiles = (n + dci::px_rows(dirs) - 1) / dci::px_rows(dirs);
+            const unsigned pgrid = (unsigned)std::min<long long>(ntiles, (long long)h->sm_count * per_sm);
+            auto go = [&](auto kern) -> int {
+                DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+                timer.start();
+                kern<<<pgrid, dci::kPxThreads, dyn, st>>>(map_x, n, h->dim, h->d_proj, I, stages, d_out, h->d_copyflag);
+                timer.stop();
+                h->launches++;
+                DCI_CUDA(cudaGetLastError());
+                h->last_projection_tma = 1;
+                return 0;
+            };
+            switch (dirs) {
+                case 8: return go(dci::project_exact_tma_kernel<8>);
+                case 12: return go(dci::project_exact_tma_kernel<12>);
+                case 20: return go(dci::project_exact_tma_kernel<20>);
+                case 32: return go(dci::project_exact_tma_kernel<32>);
+                default: return go(dci::project_exact_tma_kernel<40>);
+            }
+        }
+    }
+    h->last_projection_tma = 0;
     const unsigned grid = (unsigned)((n + dci::kProjPoints - 1) / dci::kProjPoints);
     timer.start();
     // fewest passes over the points, then the smallest accumulator count that achieves it
@@ -373,8 +414,13 @@ int dci_b200_create(dci_b200_t **out, int dim, int num_comp_indices, int num_sim
     h->sm_count = prop.multiProcessorCount;
     h->smem_optin = prop.sharedMemPerBlockOptin;
     h->smem_per_sm = prop.sharedMemPerMultiprocessor;
-    e = counted_malloc((void **)&h->d_proj, sizeof(float) * (size_t)dim * h->L * h->S);
+    // the word in which the TMA-fed exact projection reports a wait that ran out sits behind the directions
+    const size_t proj_bytes = (sizeof(float) * (size_t)dim * h->L * h->S + 255) & ~(size_t)255;
+    e = counted_malloc((void **)&h->d_proj, proj_bytes + 256);
     if (e != cudaSuccess) { delete h; return fail(DCI_B200_ERR_CUDA, "cudaMalloc(directions): %s", cudaGetErrorString(e)); }
+    h->d_copyflag = (int *)((unsigned char *)h->d_proj + proj_bytes);
+    e = cudaMemset(h->d_copyflag, 0, 256);
+    if (e != cudaSuccess) { counted_free(h->d_proj); delete h; return fail(DCI_B200_ERR_CUDA, "cudaMemset: %s", cudaGetErrorString(e)); }
     int rc = launch_directions(h, seed, 0);
     if (rc == 0 && (e = cudaDeviceSynchronize()) != cudaSuccess)
         rc = fail(DCI_B200_ERR_CUDA, "direction generation: %s", cudaGetErrorString(e));
@@ -762,7 +808,10 @@ int dci_b200_query_host(dci_b200_t *h, const float *h_query, int num_queries, in
     if (rc) return rc;
     DCI_CUDA(cudaMemcpyAsync(h_ids, h->hids.p, obytes, cudaMemcpyDeviceToHost, 0));
     DCI_CUDA(cudaMemcpyAsync(h_dists, h->hdists.p, obytes, cudaMemcpyDeviceToHost, 0));
+    int copy_flag = 0;
+    DCI_CUDA(cudaMemcpyAsync(&copy_flag, h->d_copyflag, sizeof(int), cudaMemcpyDeviceToHost, 0));
     DCI_CUDA(cudaStreamSynchronize(0));
+    if (copy_flag) return fail(DCI_B200_ERR_CUDA, "exact projection: a wait on a TMA copy ran out; keys may be incomplete");
     return 0;
 }
 
@@ -859,11 +908,13 @@ int dci_b200_set_max_ctas(dci_b200_t *h, int max_ctas) {
 
 int dci_b200_set_projection(dci_b200_t *h, int mode) {
     if (int rc = check_handle(h)) return rc;
-    if (mode < 0 || mode > 3)
+    if (mode < 0 || mode > 4)
         return fail(DCI_B200_ERR_ARG, "projection mode must be 0 (exact), 1 (tensor cores, persistent TMA pipeline), "
-                                      "2 (tensor cores, plain loads) or 3 (tensor cores, one TMA-fed tile per CTA)");
+                                      "2 (tensor cores, plain loads), 3 (tensor cores, one TMA-fed tile per CTA) or "
+                                      "4 (exact, rows staged by the computing threads only)");
     if (h->num_points > 0) return fail(DCI_B200_ERR_STATE, "the projection mode cannot change while the index holds points; clear first");
-    h->projection_mode = mode;
+    h->projection_mode = mode == 4 ? 0 : mode;      // modes 0 and 4 give the same keys, bit for bit
+    h->exact_tma = mode == 4 ? 0 : 1;
     return 0;
 }
 

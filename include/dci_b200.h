@@ -226,8 +226,14 @@ int dci_b200_set_max_ctas(dci_b200_t *h, int max_ctas);
  * per CTA.  Keys of modes 1-3 differ from mode 0 by about
  * 1e-6 * |x|, which can move a point across a window boundary, so results are
  * not guaranteed identical to mode 0.  Modes 1-3 synchronise the stream after
- * each projection to check its bounded waits.  Rejected while the index holds
- * points (data and queries must be projected the same way). */
+ * each projection to check its bounded waits.  In mode 0, inputs of at least
+ * 1024 rows whose dim is a multiple of 4 (16-byte aligned base, at most 40
+ * directions) are streamed into shared memory by TMA copies; mode 4 is mode 0
+ * with the rows always staged by the computing threads -- the same keys, bit
+ * for bit.  A bounded wait of the TMA-fed mode-0 kernel that runs out is
+ * reported by the next dci_b200_query_host (DCI_B200_ERR_CUDA).  Rejected
+ * while the index holds points (data and queries must be projected the same
+ * way). */
 int dci_b200_set_projection(dci_b200_t *h, int mode);
 
 /* When enabled, every later query brackets its kernels with CUDA events on the

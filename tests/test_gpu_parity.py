@@ -72,16 +72,28 @@ def test_directions_unit_norm_and_seeded():
     assert abs(float(corr)) < 0.08
 
 
-@pytest.mark.parametrize("n,dim,L,S", [(1000, 100, 2, 7), (777, 37, 3, 12), (5000, 128, 2, 10), (300, 960, 3, 12), (64, 8, 1, 1)])
+@pytest.mark.parametrize("n,dim,L,S", [(1000, 100, 2, 7), (777, 37, 3, 12), (5000, 128, 2, 10), (300, 960, 3, 12), (64, 8, 1, 1),
+                                       # at least 1024 rows of a multiple of 4 coordinates: rows streamed by TMA copies
+                                       (3001, 100, 2, 6), (1500, 36, 1, 8), (2049, 960, 3, 12), (1025, 8, 1, 1),
+                                       (70000, 96, 2, 10), (4100, 256, 2, 15), (4096, 44, 4, 10),
+                                       (2000, 130, 2, 5), (3000, 128, 6, 7)])      # dim % 4 != 0, more than 40 directions
 def test_projection_bit_exact(n, dim, L, S):
     from dciknn_cuda_b200 import DCI
     rng = np.random.default_rng(n)
     x = rng.standard_normal((n, dim)).astype(np.float32)
     proj = cases.unit_rows(rng, L * S, dim)
-    g = DCI(dim, L, S, proj=torch.from_numpy(proj))
-    got = g.project(torch.from_numpy(x).cuda()).cpu().numpy()
     want = oracle.project(proj, x)
-    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    xd = torch.from_numpy(x).cuda()
+    for mode in ("exact", "exact_plain"):
+        g = DCI(dim, L, S, proj=torch.from_numpy(proj))
+        g.set_projection(mode)
+        got = g.project(xd).cpu().numpy()
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), mode
+        if mode == "exact":       # an unaligned view of the same rows takes the other kernel
+            pad = torch.empty(n * dim + 1, device="cuda")
+            pad[1:] = xd.reshape(-1)
+            got = g.project(pad[1:].view(n, dim)).cpu().numpy()
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
 
 
 @pytest.mark.parametrize("N,P", [(2000, 100), (103, 10), (13, 40), (10000, 1), (30000, 2), (70000, 1), (140000, 2)])
@@ -153,6 +165,17 @@ def test_large_partition_global_scratch_path():
     for max_ctas in (0, 1):
         _, _, ids, dists, oi, od, gs, os_ = _run_both(c, max_ctas=max_ctas)
         _assert_same(ids, dists, oi, od, gs, os_, "global-scratch")
+
+
+@pytest.mark.parametrize("n", [65526, 65530])
+def test_partition_sizes_around_the_16_bit_position_limit(n):
+    """Positions are kept in 16 bits while ppb + T <= 65536 (a position plus the offset of the window
+    grid must fit): 65 526 points with T = 10 are the largest such partition, 65 530 take 32 bits."""
+    rng = np.random.default_rng(n)
+    c = dict(data=cases.latent_linear(rng, n, 8, 16, 0.01), query=cases.latent_linear(rng, 4, 8, 16, 0.01),
+             L=2, S=3, P=1, T=10, k=10, outer=5000, max_cand=None, proj=cases.unit_rows(rng, 6, 16))
+    _, _, ids, dists, oi, od, gs, os_ = _run_both(c)
+    _assert_same(ids, dists, oi, od, gs, os_, "position limit")
 
 
 def test_wide_rank_path():
