@@ -100,10 +100,11 @@ build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_in
             };
             int over = usable ? 0 : 1;
             if (usable)
-                for (int x = threadIdx.x; x < n; x += blockDim.x)
-                    slot[x] = (uint8_t)min(bucket_arrive(hist, bucket(kA[x])), 255u);
-            __syncthreads();
-            for (int j = threadIdx.x; j < nbuckets; j += blockDim.x) over |= ((uint32_t)hist[j] > (uint32_t)kMaxBucket);
+                for (int x = threadIdx.x; x < n; x += blockDim.x) {
+                    const uint32_t arrival = bucket_arrive(hist, bucket(kA[x]));
+                    over |= (arrival >= (uint32_t)kMaxBucket);      // the arrival that makes a bucket too large reports it
+                    slot[x] = (uint8_t)min(arrival, 255u);
+                }
             over = __syncthreads_or(over);
             if (!over) {
                 cta_bucket_place_and_rank<ValT, ValT>(kA, n, slot, vA, kB, hist, nbuckets, bucket, warp_tot, vB,
@@ -124,12 +125,26 @@ build_segments_kernel(const float *__restrict__ keys_unsorted, int N, int num_in
             cta_radix_sort<ValT, ValT, false>(kA, vA, kB, vB, n, hist, warp_tot, (ValT *)nullptr);
         }
         const int qn = n / T, rem = n % T;
+        // every output array is written in its own order, so that the stores of a warp are contiguous:
+        // the stride-T keys residue class by residue class (while T is small enough for that to keep
+        // the threads busy), the positions from the ranks, which are indexed by point
         for (int x = threadIdx.x; x < n; x += blockDim.x) {
-            const int r = x % T, j = x / T;
-            skeysT[row + r * qn + min(r, rem) + j] = ordered_to_float(ks[x]);
             skeys[row + x] = ordered_to_float(ks[x]);
             sids[row + x] = (int)(lo + vs[x]);
-            spos[prow + vs[x]] = (ValT)x;
+            if (ranked) spos[prow + x] = vB[x];
+            else spos[prow + vs[x]] = (ValT)x;
+        }
+        if (T <= 64) {
+            for (int r = 0; r < T; ++r) {
+                const size_t base = row + (size_t)r * qn + min(r, rem);
+                const int cnt = qn + (r < rem ? 1 : 0);
+                for (int j = threadIdx.x; j < cnt; j += blockDim.x) skeysT[base + j] = ordered_to_float(ks[j * T + r]);
+            }
+        } else {
+            for (int x = threadIdx.x; x < n; x += blockDim.x) {
+                const int r = x % T, j = x / T;
+                skeysT[row + r * qn + min(r, rem) + j] = ordered_to_float(ks[x]);
+            }
         }
         for (int x = n + threadIdx.x; x < pos_stride(ppb); x += blockDim.x) spos[prow + x] = (ValT)0;
         __syncthreads();
