@@ -692,13 +692,14 @@ traverse_kernel(const TraverseParams prm) {
         };
         // a pass of several pairs per thread while the points still to do fill most of it, passes of
         // one pair for the rest and for small partitions (32-bit positions take two registers a pair,
-        // so their large pass has fewer pairs)
+        // so their large pass has fewer pairs; so has the one for T = 1, whose five-pair instance
+        // made the compiler spill registers in the instance that every T > 1 uses)
         auto promote = [&](auto t_is_one) {
             const int pair_step = 2 * (int)blockDim.x;
             for (int p0 = 0; p0 < n;) {
                 const int units = (n - p0 + pair_step - 1) / pair_step;
                 // pairs of the large pass; none where the registers are needed elsewhere (query groups)
-                constexpr int kBig = BATCH ? 0 : (sizeof(PosT) != 2 ? 2 : (SMEM ? 5 : 4));
+                constexpr int kBig = BATCH ? 0 : ((decltype(t_is_one)::value || sizeof(PosT) != 2) ? 2 : (SMEM ? 5 : 4));
                 if (kBig > 1 && units >= 2) {
                     // a full pass, or for a short rest the same pass by as many warps as it takes
                     int step = pair_step;
