@@ -358,18 +358,19 @@ int launch_traverse(dci_b200 *h, dci::TraverseParams prm, int nthreads, cudaStre
     DCI_CUDA(h->scratch.ensure(per_cta * grid));
     prm.gscratch = (unsigned char *)h->scratch.p;
     prm.gscratch_per_cta = per_cta;
+    // the common case has kernel instances of its own, without the code of the rarer paths
+    const bool lean = !prm.blind && !prm.topk_global && prm.vec8 && !prm.work_stats && !prm.phase_cycles && prm.T > 1;
+    auto go = [&](auto kern) -> int {
+        DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+        kern<<<grid, nthreads, dyn, st>>>(prm);
+        return 0;
+    };
     if (smem && prm.qbatch > 1) {
-        auto kern = dci::traverse_kernel<ValT, PosT, true, true>;
-        DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-        kern<<<grid, nthreads, dyn, st>>>(prm);
+        if (int rc = lean ? go(dci::traverse_kernel<ValT, PosT, true, true, true>) : go(dci::traverse_kernel<ValT, PosT, true, true>)) return rc;
     } else if (smem) {
-        auto kern = dci::traverse_kernel<ValT, PosT, true, false>;
-        DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-        kern<<<grid, nthreads, dyn, st>>>(prm);
+        if (int rc = lean ? go(dci::traverse_kernel<ValT, PosT, true, false, true>) : go(dci::traverse_kernel<ValT, PosT, true, false>)) return rc;
     } else {
-        auto kern = dci::traverse_kernel<ValT, PosT, false, false>;
-        DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-        kern<<<grid, nthreads, dyn, st>>>(prm);
+        if (int rc = lean ? go(dci::traverse_kernel<ValT, PosT, false, false, true>) : go(dci::traverse_kernel<ValT, PosT, false, false>)) return rc;
     }
     h->launches++;
     DCI_CUDA(cudaGetLastError());

@@ -324,9 +324,17 @@ __device__ __forceinline__ int window_visit_order(int g, int nl, int sp) {
 // BATCH: compile the query-group path (Q > 1 with the dense distance pass).  The host picks it
 // when the configuration makes exhaustive work items likely; without it the kernel is the plain
 // one-query-per-pass loop.
-template <typename ValT, typename PosT, bool SMEM, bool BATCH>
+// LEAN: the instance for the common case -- distances wanted (not blind), selection buffers in shared
+// memory, 256-bit row loads, T > 1, no work statistics and no phase counters -- so that the code of
+// the rarer paths does not weigh on its register allocation and instruction cache.
+template <typename ValT, typename PosT, bool SMEM, bool BATCH, bool LEAN = false>
 __global__ void __launch_bounds__(1024, 1)
 traverse_kernel(const TraverseParams prm) {
+    const bool f_blind = LEAN ? false : prm.blind != 0;
+    const bool f_topk_global = LEAN ? false : prm.topk_global != 0;
+    const bool f_vec8 = LEAN ? true : prm.vec8 != 0;
+    long long *const f_work_stats = LEAN ? nullptr : prm.work_stats;
+    unsigned long long *const f_phase_cycles = LEAN ? nullptr : (unsigned long long *)prm.phase_cycles;
     extern __shared__ __align__(16) unsigned char dyn_smem[];
     __shared__ int s_pos[kMaxIndices];       // last position with key < q
     __shared__ int s_nl[kMaxIndices];        // number of left windows
@@ -349,8 +357,8 @@ traverse_kernel(const TraverseParams prm) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nw = blockDim.x >> 5;
     const int L = prm.L, S = prm.S, T = prm.T, I = L * S, N = prm.N, dim = prm.dim;
     const TraverseLayout<ValT> lay =
-        TraverseLayout<ValT>::make(blockDim.x, dim, prm.topk_global ? 0 : prm.topk_cap, L, prm.wcap, prm.ppb,
-                                   prm.nbuckets, SMEM && prm.vec4 && !prm.vec8, prm.bkey != 0);
+        TraverseLayout<ValT>::make(blockDim.x, dim, f_topk_global ? 0 : prm.topk_cap, L, prm.wcap, prm.ppb,
+                                   prm.nbuckets, SMEM && prm.vec4 && !f_vec8, prm.bkey != 0);
     ValT *cnt = reinterpret_cast<ValT *>(dyn_smem);                    // bucket counters / radix histogram
     float *qvec = reinterpret_cast<float *>(dyn_smem + lay.cnt_bytes);
     unsigned char *slab = prm.gscratch + (size_t)blockIdx.x * prm.gscratch_per_cta;
@@ -372,7 +380,7 @@ traverse_kernel(const TraverseParams prm) {
     uint32_t *kenc = reinterpret_cast<uint32_t *>(uni);                       // best promotion per point
     ValT *list = reinterpret_cast<ValT *>(uni + lay.list_off);                // lane-0 ranks, then candidates
     // distance view
-    uint64_t *topk_bufs = prm.topk_global ? reinterpret_cast<uint64_t *>(slab + prm.topk_global_off)
+    uint64_t *topk_bufs = f_topk_global ? reinterpret_cast<uint64_t *>(slab + prm.topk_global_off)
                                           : reinterpret_cast<uint64_t *>(uni);   // over kenc, phase 5 only
     float *tiles = reinterpret_cast<float *>(uni + lay.topk_bytes);           // staging, shared variant only
     const PosT *spos = reinterpret_cast<const PosT *>(prm.spos);
@@ -386,9 +394,9 @@ traverse_kernel(const TraverseParams prm) {
     const long long nwork = (long long)ngroups * prm.num_parts;
     long long t_last = 0;
 #define DCI_PHASE_MARK(slot_)                                                             \
-    if (prm.phase_cycles && tid == 0) {                                                   \
+    if (f_phase_cycles && tid == 0) {                                                   \
         const long long now_ = clock64();                                                 \
-        atomicAdd((unsigned long long *)&prm.phase_cycles[slot_], (unsigned long long)(now_ - t_last)); \
+        atomicAdd(&f_phase_cycles[slot_], (unsigned long long)(now_ - t_last)); \
         t_last = now_;                                                                    \
     }
 
@@ -401,7 +409,7 @@ traverse_kernel(const TraverseParams prm) {
         const int ql = grp * Q + jq;
         if (ql >= prm.nq) break;
         const int q = prm.q0 + ql;
-        if (prm.phase_cycles && tid == 0) t_last = clock64();
+        if (f_phase_cycles && tid == 0) t_last = clock64();
 
         for (int i = tid; i < I; i += blockDim.x) s_qp[i] = prm.qproj[(size_t)i * prm.nq_total + q];
         for (int c = tid; c < dim; c += blockDim.x) qvec[c] = prm.query[(size_t)q * dim + c];
@@ -709,7 +717,7 @@ traverse_kernel(const TraverseParams prm) {
                 } else { promote_pass(t_is_one, IntTag<1>{}, p0, pair_step); p0 += pair_step; }
             }
         };
-        if (T == 1) promote(TrueTag{}); else promote(FalseTag{});
+        if (!LEAN && T == 1) promote(TrueTag{}); else promote(FalseTag{});
         __syncthreads();
 
         DCI_PHASE_MARK(3)
@@ -736,7 +744,7 @@ traverse_kernel(const TraverseParams prm) {
             stop = min(stop_rule, limit - 1);
         }
         int lane0_stat = 0;
-        if (prm.work_stats) {
+        if (f_work_stats) {
             int c = 0;
             for (int j = tid; j < cnt0; j += blockDim.x) c += ((long long)list[j] <= stop);
             lane0_stat = cta_sum(c, s_scratch);
@@ -767,7 +775,7 @@ traverse_kernel(const TraverseParams prm) {
         __syncthreads();
         const int ncand = s_count[1];
 
-        if (prm.work_stats) {
+        if (f_work_stats) {
             long long visits = 0;
             int entries = 0;
             for (int m = 0; m < L; ++m) {
@@ -785,7 +793,7 @@ traverse_kernel(const TraverseParams prm) {
             }
             entries = cta_sum(entries, s_scratch);
             if (tid == 0) {
-                long long *st = prm.work_stats + ((size_t)q * prm.P + b) * 6;
+                long long *st = f_work_stats + ((size_t)q * prm.P + b) * 6;
                 // the reference's loop runs out of windows at iteration maxW unless its stop test or its
                 // iteration bound ends it first
                 const bool exhausted = stop_rule > (long long)maxW && (long long)maxW < limit;
@@ -798,7 +806,7 @@ traverse_kernel(const TraverseParams prm) {
         if (BATCH && Q > 1 && ncand == n) {   // every point promoted: distances in the shared pass below
             if (tid == 0) {
                 s_dense[ndense] = ql;
-                if (prm.phase_cycles) atomicAdd((unsigned long long *)&prm.phase_cycles[15], 1ull);
+                if (f_phase_cycles) atomicAdd(&f_phase_cycles[15], 1ull);
             }
             ++ndense;
             __syncthreads();
@@ -810,7 +818,7 @@ traverse_kernel(const TraverseParams prm) {
         // best such bound published so far can be dropped (strictly farther, so ties are kept).
         // Which partitions have published depends on timing; the merged result does not.
         float bound_d = __int_as_float(0x7F800000), bound_sq = bound_d;
-        if (prm.qbound && !prm.blind) {
+        if (prm.qbound && !f_blind) {
             const uint32_t bb = *reinterpret_cast<volatile uint32_t *>(prm.qbound + ql);
             if (bb < 0x7F7F7F7Fu) {                                  // the buffer starts as 0x7F7F7F7F: no bound yet
                 bound_d = __uint_as_float(bb);
@@ -823,12 +831,12 @@ traverse_kernel(const TraverseParams prm) {
         for (int base = 0; base < ncand; base += blockDim.x) {
             uint64_t key = kEmptySlot;
             const int j = base + tid;
-            if (prm.blind) {             // blind querying (reference :398-399): order of retrieval, no row is read
+            if (f_blind) {             // blind querying (reference :398-399): order of retrieval, no row is read
                 if (j < ncand) {
                     const uint32_t p = (uint32_t)list[j];
                     key = ((uint64_t)(kenc[p] >> prm.tshift) << 32) | (uint32_t)(lo + p);
                 }
-            } else if (prm.vec8) {
+            } else if (f_vec8) {
                 if (j < ncand) {
                     const long long gid = lo + (long long)list[j];
                     const float d = dist_sequential_v8(prm.data + (size_t)gid * dim, qvec, dim, bound_sq);
@@ -851,17 +859,17 @@ traverse_kernel(const TraverseParams prm) {
         uint64_t *out = prm.part_topk + ((size_t)ql * prm.num_parts + b) * prm.kpart;
         const uint64_t *res = topk.result();
         for (int j = tid; j < prm.kpart; j += blockDim.x) out[j] = res[j];
-        if (tid == 0 && prm.qbound && !prm.blind && prm.kpart == prm.knn && res[prm.knn - 1] != kEmptySlot)
+        if (tid == 0 && prm.qbound && !f_blind && prm.kpart == prm.knn && res[prm.knn - 1] != kEmptySlot)
             atomicMin(prm.qbound + ql, (uint32_t)(res[prm.knn - 1] >> 32));
         __syncthreads();
         DCI_PHASE_MARK(6)
-        if (prm.phase_cycles && tid == 0) atomicAdd((unsigned long long *)&prm.phase_cycles[15], 1ull);
+        if (f_phase_cycles && tid == 0) atomicAdd(&f_phase_cycles[15], 1ull);
       }   // queries of the group
 
       // ---- 5'. dense distance pass for the deferred queries (host enables Q > 1 only with
       // 256-bit row loads, shared-memory buffers and room for Q selection buffer pairs)
       if (BATCH && ndense > 0) {
-        if (prm.phase_cycles && tid == 0) t_last = clock64();
+        if (f_phase_cycles && tid == 0) t_last = clock64();
         const size_t tk_bytes = (size_t)prm.dense_cap * 16;                      // two halves of u64[dense_cap]
         // the query vectors coordinate-major, kMaxQBatch slots per coordinate: one 128-bit load brings
         // one coordinate of four queries, i.e. two packed operands
