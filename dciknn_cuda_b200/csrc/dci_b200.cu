@@ -1289,8 +1289,12 @@ int query_noalloc_impl(dci_b200 *h, dci::TraverseParams prm, int nthreads, unsig
                            : nullptr;
     const int merge_threads = 256;
     const int merge_cap = next_pow2(prm.knn + merge_threads);
-    if (smem) DCI_CUDA(cudaFuncSetAttribute(dci::traverse_kernel<ValT, PosT, true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
-    else DCI_CUDA(cudaFuncSetAttribute(dci::traverse_kernel<ValT, PosT, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
+    // the same kernel instances as the regular query
+    const bool lean = !prm.blind && !prm.topk_global && prm.vec8 && !prm.work_stats && !prm.phase_cycles && prm.T > 1;
+    void (*kern)(const dci::TraverseParams) =
+        smem ? (lean ? dci::traverse_kernel<ValT, PosT, true, false, true> : dci::traverse_kernel<ValT, PosT, true, false, false>)
+             : (lean ? dci::traverse_kernel<ValT, PosT, false, false, true> : dci::traverse_kernel<ValT, PosT, false, false, false>);
+    DCI_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dyn));
     for (int q0 = 0; q0 < num_queries; q0 += batch) {
         prm.q0 = q0;
         prm.nq = std::min(batch, num_queries - q0);
@@ -1299,8 +1303,7 @@ int query_noalloc_impl(dci_b200 *h, dci::TraverseParams prm, int nthreads, unsig
             DCI_CUDA(cudaMemsetAsync(qbound, 0x7F, sizeof(uint32_t) * (size_t)prm.nq, st));
         }
         const unsigned grid = (unsigned)std::min<long long>((long long)prm.nq * prm.num_parts, max_grid);
-        if (smem) dci::traverse_kernel<ValT, PosT, true, false><<<grid, nthreads, dyn, st>>>(prm);
-        else dci::traverse_kernel<ValT, PosT, false, false><<<grid, nthreads, dyn, st>>>(prm);
+        kern<<<grid, nthreads, dyn, st>>>(prm);
         h->launches++;
         DCI_CUDA(cudaGetLastError());
         dci::merge_partitions_kernel<<<prm.nq, merge_threads, (size_t)merge_cap * 16, st>>>(
