@@ -342,6 +342,29 @@ def time_steps(R, step, steps, warmup):
     return R.max_over_ranks(mine), R.all_values(mine), out
 
 
+def other_build_times(device):
+    """Index build (`add`, warm buffers) of one shard of the two multi-GPU configurations, whose headline
+    includes the build: device-generated rows of the same shape (the build does not depend on the values'
+    distribution beyond the ties it meets)."""
+    from dciknn_cuda_b200 import DCI
+    res = {}
+    for name in ("configs3_shard", "configs4_shard"):
+        c = WORKLOADS[name]
+        x = torch.randn(c["n_points"], c["dim"], device="cuda:%d" % device)
+        g = DCI(c["dim"], c["L"], c["S"], c["P"], c["T"], device, seed=7)
+        g.add(x); torch.cuda.synchronize()
+        ts = []
+        for _ in range(3):
+            g.clear()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); g.add(x); e1.record(); torch.cuda.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        res[name] = {"points": c["n_points"], "dim": c["dim"], "simple_indices": c["L"] * c["S"], "add_ms": statistics.median(ts)}
+        del g, x
+        torch.cuda.empty_cache()
+    return res
+
+
 def sharded_10m(R, args):
     """The strong-scaling block: one 10M x 96 mixture index over the ranks (reference sharding rule)."""
     from dciknn_cuda_b200 import DCI, MDCI
@@ -593,6 +616,8 @@ def bench_ours(args):
         }
     del engine, local_dci, data
     torch.cuda.empty_cache()
+    if out is not None and world == 1 and args.workload == "configs1" and not args.no_sharded:
+        out["build_ms_other_shapes"] = other_build_times(local)
     block = None
     if not args.no_sharded and args.workload == "configs1":
         block = sharded_10m(R, args)
