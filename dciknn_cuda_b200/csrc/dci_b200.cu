@@ -812,7 +812,10 @@ int dci_b200_query_host(dci_b200_t *h, const float *h_query, int num_queries, in
     int copy_flag = 0;
     DCI_CUDA(cudaMemcpyAsync(&copy_flag, h->d_copyflag, sizeof(int), cudaMemcpyDeviceToHost, 0));
     DCI_CUDA(cudaStreamSynchronize(0));
-    if (copy_flag) return fail(DCI_B200_ERR_CUDA, "exact projection: a wait on a TMA copy ran out; keys may be incomplete");
+    if (copy_flag) {      // reported once; the projection that set it (data or queries) has to be repeated
+        cudaMemsetAsync(h->d_copyflag, 0, sizeof(int), 0);
+        return fail(DCI_B200_ERR_CUDA, "exact projection: a wait on a TMA copy ran out; keys may be incomplete");
+    }
     return 0;
 }
 
